@@ -1,0 +1,157 @@
+/*
+ * tetris_b200.h -- C ABI of the B200 (sm_100a) sparse-filter convolution engine.
+ *
+ * Plain C: pointers, sizes and ints only.  Every entry point returns a status
+ * code (TETRIS_OK == 0) instead of printing and calling exit() as the
+ * reference's checkCudaErrors does (Tetris/cuda_utils.h:9-16); the text of the
+ * last failure on the calling thread is available from tetris_last_error().
+ *
+ * What each entry point replaces in the reference (paths inside that project):
+ *   tetris_filter_create*     SparseFilter<float,int,int> constructor: compress +
+ *                             reorder + upload, Tetris/spconv2d_utils.h:25-265
+ *   tetris_filter_destroy     ~SparseFilter, Tetris/spconv2d_utils.h:267-273
+ *   tetris_filter_info/
+ *   tetris_filter_download    the public fields and Get*() getters,
+ *                             Tetris/spconv2d_utils.h:495-514
+ *   tetris_conv2d_launch      SparseConv2d<...>() launcher,
+ *                             Tetris/spconv2d_kernel.cu:163-188
+ *   tetris_conv2d_time        TimingTetrisSparseConv2d, Tetris/spconv2d.cc:29-69
+ *   tetris_conv2d_host        CudaSparseConv2d's data path (host NCHW in, host
+ *                             NCHW out), Tetris/spconv2d.cc:332-367
+ *   tetris_nchw_to_nhwc/
+ *   tetris_nhwc_to_nchw       NCHW2NHWC / NHWC2NCHW, Tetris/tensor_utils.cc:85-111,
+ *                             done on the device
+ *   tetris_conv2d_host_sharded  no counterpart (the reference pins device 0,
+ *                             Tetris/spconv2d.cc:379-380): batch slices of one
+ *                             call run on several GPUs of one box
+ */
+#ifndef TETRIS_B200_H_
+#define TETRIS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  TETRIS_OK = 0,
+  TETRIS_ERR_INVALID = 1,     /* bad argument (null pointer, bad shape, ...)       */
+  TETRIS_ERR_CUDA = 2,        /* a CUDA runtime call failed; see tetris_last_error */
+  TETRIS_ERR_UNSUPPORTED = 3, /* shape outside what the kernels cover              */
+  TETRIS_ERR_NOMEM = 4        /* host or device allocation failed                  */
+};
+
+/* Kernel variants accepted by tetris_conv2d_launch_ex. */
+enum {
+  TETRIS_VARIANT_AUTO = 0,    /* fastest kernel that covers the shape              */
+  TETRIS_VARIANT_GENERIC = 1, /* one thread per output pixel, any KS/stride        */
+  TETRIS_VARIANT_TILED = 2    /* shared-memory tile + register-blocked interpreter */
+};
+
+typedef struct tetris_filter tetris_filter_t; /* opaque; owns device buffers */
+
+/* Compression options; zero in a field means "engine default". */
+typedef struct {
+  int oc_block;  /* output channels per program (register block), 8 or 16          */
+  int tile_ic;   /* input channels per stage, multiple of 4, <= 64                 */
+  int reserved[6];
+} tetris_filter_opts_t;
+
+typedef struct {
+  int in_channel, out_channel, kernel_size, groups;
+  int oc_block, tile_ic;
+  int n_oc_blocks;        /* ceil(out_channel / oc_block)                          */
+  int n_stages;           /* ceil(in_channel / tile_ic)                            */
+  int64_t nnz;            /* nonzero weights, padding excluded                     */
+  int64_t n_ops;          /* 8-byte records in the compressed program stream       */
+  int64_t compressed_bytes; /* device bytes held: ops + program offsets            */
+  int device;
+  int reserved[7];
+} tetris_filter_info_t;
+
+/*
+ * Compress a dense OIHW FP32 filter (host pointer, borrowed, read-only) on
+ * `device` and keep the result there.  groups == 1, or groups == in_channel ==
+ * out_channel (depthwise; filter is [C][1][KS][KS]).  The dense filter is
+ * copied to the device and compressed there by CUDA kernels; nothing is
+ * compressed on the host.
+ */
+int tetris_filter_create(const float *filter_oihw, int in_channel, int out_channel,
+                         int kernel_size, int groups, int device, tetris_filter_t **out);
+int tetris_filter_create_ex(const float *filter_oihw, int in_channel, int out_channel,
+                            int kernel_size, int groups, int device,
+                            const tetris_filter_opts_t *opts, tetris_filter_t **out);
+void tetris_filter_destroy(tetris_filter_t *f);
+int tetris_filter_info(const tetris_filter_t *f, tetris_filter_info_t *info);
+
+/*
+ * Copy the compressed form back to the host: `ops` receives n_ops 8-byte
+ * records, `prog_offsets` receives n_oc_blocks * n_stages + 1 record indices.
+ * Either pointer may be NULL to skip that array.
+ */
+int tetris_filter_download(const tetris_filter_t *f, uint64_t *ops, size_t ops_capacity,
+                           int32_t *prog_offsets, size_t offsets_capacity);
+
+/*
+ * Convolution, device pointers, NHWC in and NHWC out as in the reference
+ * launcher; asynchronous on `stream` (a cudaStream_t, may be NULL); allocates
+ * nothing; the output is fully overwritten.  The device of `f` must be current.
+ */
+int tetris_conv2d_launch(const tetris_filter_t *f, const float *d_input_nhwc,
+                         float *d_output_nhwc, int batch_size, int img_h, int img_w,
+                         int stride, int padding, void *stream);
+int tetris_conv2d_launch_ex(const tetris_filter_t *f, const float *d_input_nhwc,
+                            float *d_output_nhwc, int batch_size, int img_h, int img_w,
+                            int stride, int padding, void *stream, int variant);
+
+/*
+ * The reference's timing protocol: `warm` untimed launches, a device
+ * synchronise, then `repeat` back-to-back launches between two events on
+ * `stream`; *ms_mean = elapsed / repeat.
+ */
+int tetris_conv2d_time(const tetris_filter_t *f, const float *d_input_nhwc,
+                       float *d_output_nhwc, int batch_size, int img_h, int img_w, int stride,
+                       int padding, void *stream, int variant, int warm, int repeat,
+                       float *ms_mean);
+
+/*
+ * Host NCHW in, host NCHW out, blocking.  Copies the input to the device,
+ * transposes it to NHWC there, runs the convolution, transposes back and
+ * copies the result out.  Device buffers are allocated and freed inside.
+ * `h_input` is not modified.
+ */
+int tetris_conv2d_host(const tetris_filter_t *f, const float *h_input_nchw,
+                       float *h_output_nchw, int batch_size, int img_h, int img_w, int stride,
+                       int padding, void *stream);
+
+/* Device-side layout transposes (out of place), asynchronous on `stream`. */
+int tetris_nchw_to_nhwc(const float *d_src, float *d_dst, int N, int C, int H, int W,
+                        void *stream);
+int tetris_nhwc_to_nchw(const float *d_src, float *d_dst, int N, int C, int H, int W,
+                        void *stream);
+
+/*
+ * Batch partitioner: `filters[g]` is the same filter compressed on GPU g
+ * (g < n_gpus).  The batch is cut into contiguous slices, slice g runs on the
+ * device of filters[g] through tetris_conv2d_host from its own host thread; no
+ * collective is involved.  Returns the first failing shard's status.
+ */
+int tetris_conv2d_host_sharded(tetris_filter_t *const *filters, int n_gpus,
+                               const float *h_input_nchw, float *h_output_nchw,
+                               int batch_size, int img_h, int img_w, int stride, int padding);
+
+/* Contiguous batch slice [*begin, *begin + *count) of shard `rank` out of `world`. */
+int tetris_batch_slice(int batch_size, int world, int rank, int *begin, int *count);
+
+/* SM count, SM clock (kHz) and FP32 FMA lanes per SM of `device`. */
+int tetris_device_info(int device, int *sm_count, int *sm_clock_khz, int *fp32_lanes_per_sm);
+
+/* Text of the last error raised on this thread ("" if none). */
+const char *tetris_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TETRIS_B200_H_ */

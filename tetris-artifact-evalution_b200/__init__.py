@@ -1,0 +1,266 @@
+"""B200 sparse-filter convolution engine: Python host side over the C ABI.
+
+The directory name carries a hyphen, so load the package by path:
+
+    import importlib.util, sys
+    spec = importlib.util.spec_from_file_location(
+        "tetris_b200", "tetris-artifact-evalution_b200/__init__.py",
+        submodule_search_locations=["tetris-artifact-evalution_b200"])
+    tetris_b200 = importlib.util.module_from_spec(spec)
+    sys.modules["tetris_b200"] = tetris_b200
+    spec.loader.exec_module(tetris_b200)
+
+Names mirror the reference's host API for this path:
+
+    SparseFilter        <- SparseFilter<float,int,int>   (Tetris/spconv2d_utils.h:23-515)
+    sparse_conv2d       <- SparseConv2d<...> launcher     (Tetris/spconv2d_kernel.cu:163-188)
+    timing_sparse_conv2d<- TimingTetrisSparseConv2d       (Tetris/spconv2d.cc:29-69)
+    cuda_sparse_conv2d  <- CudaSparseConv2d               (Tetris/spconv2d.cc:332-367)
+
+Everything computes on the GPU through libtetris_b200.so.  There is no CPU
+fallback: if the library is missing or fails to load, importing `lib()` raises.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtetris_b200.so")
+
+WARM = 30     # Tetris/tensor_utils.h:11
+REPEAT = 100  # Tetris/tensor_utils.h:10
+
+VARIANT_AUTO, VARIANT_GENERIC, VARIANT_TILED = 0, 1, 2
+
+_c_float_p = ctypes.POINTER(ctypes.c_float)
+_c_int_p = ctypes.POINTER(ctypes.c_int)
+
+
+class FilterOpts(ctypes.Structure):
+    _fields_ = [("oc_block", ctypes.c_int), ("tile_ic", ctypes.c_int), ("reserved", ctypes.c_int * 6)]
+
+
+class FilterInfo(ctypes.Structure):
+    _fields_ = [
+        ("in_channel", ctypes.c_int), ("out_channel", ctypes.c_int),
+        ("kernel_size", ctypes.c_int), ("groups", ctypes.c_int),
+        ("oc_block", ctypes.c_int), ("tile_ic", ctypes.c_int),
+        ("n_oc_blocks", ctypes.c_int), ("n_stages", ctypes.c_int),
+        ("nnz", ctypes.c_int64), ("n_ops", ctypes.c_int64), ("compressed_bytes", ctypes.c_int64),
+        ("device", ctypes.c_int), ("reserved", ctypes.c_int * 7),
+    ]
+
+
+# name -> (restype, argtypes); the list must match include/tetris_b200.h
+_VP = ctypes.c_void_p
+_I = ctypes.c_int
+SIGNATURES = {
+    "tetris_filter_create": (_I, [_VP, _I, _I, _I, _I, _I, ctypes.POINTER(_VP)]),
+    "tetris_filter_create_ex": (_I, [_VP, _I, _I, _I, _I, _I, ctypes.POINTER(FilterOpts), ctypes.POINTER(_VP)]),
+    "tetris_filter_destroy": (None, [_VP]),
+    "tetris_filter_info": (_I, [_VP, ctypes.POINTER(FilterInfo)]),
+    "tetris_filter_download": (_I, [_VP, _VP, ctypes.c_size_t, _VP, ctypes.c_size_t]),
+    "tetris_conv2d_launch": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
+    "tetris_conv2d_launch_ex": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I]),
+    "tetris_conv2d_time": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _I, _I, _c_float_p]),
+    "tetris_conv2d_host": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
+    "tetris_nchw_to_nhwc": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
+    "tetris_nhwc_to_nchw": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
+    "tetris_conv2d_host_sharded": (_I, [ctypes.POINTER(_VP), _I, _VP, _VP, _I, _I, _I, _I, _I]),
+    "tetris_batch_slice": (_I, [_I, _I, _I, _c_int_p, _c_int_p]),
+    "tetris_device_info": (_I, [_I, _c_int_p, _c_int_p, _c_int_p]),
+    "tetris_last_error": (ctypes.c_char_p, []),
+}
+
+_lib = None
+
+
+class TetrisError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, status, message):
+        super().__init__("tetris_b200 status %d: %s" % (status, message))
+        self.status = status
+
+
+def lib():
+    """The loaded native library.  Raises if it is absent: there is no other compute path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                "%s is missing: build it with `python %s` (needs nvcc); the engine has no "
+                "fallback path" % (LIB_PATH, os.path.join(_HERE, "build.py")))
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def _check(status):
+    if status != 0:
+        raise TetrisError(status, lib().tetris_last_error().decode("utf-8", "replace"))
+
+
+def _ptr(x):
+    """Device or host address of a torch tensor, numpy array, int or None."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    if isinstance(x, np.ndarray):
+        return x.ctypes.data
+    raise TypeError("cannot take the address of %r" % type(x))
+
+
+def _stream_ptr(stream):
+    if stream is None:
+        return None
+    return getattr(stream, "cuda_stream", stream)
+
+
+def out_extent(size, kernel_size, stride, padding):
+    """Output extent, Tetris/spconv2d.cc:339-340."""
+    return (size + 2 * padding - kernel_size) // stride + 1
+
+
+class SparseFilter:
+    """Compressed filter living on one GPU.
+
+    Constructor arguments follow the reference class (Tetris/spconv2d_utils.h:25-27):
+    dense OIHW float32 `filter`, `in_channel`, `out_channel`, `kernel_size`, then
+    `TILE_IC` (input channels per stage; 0 = engine default).  `apply_reorder` and
+    `apply_vectorize` are accepted for call compatibility: the new format always
+    groups weights by shared input offset and always uses vector loads.  `groups`
+    and `device` are additions.  Like the reference object it owns device memory
+    (freed by close() / garbage collection) and must not be copied.
+    """
+
+    def __init__(self, filter, in_channel, out_channel, kernel_size, TILE_IC=0,
+                 apply_reorder=True, apply_vectorize=True, groups=1, device=0, oc_block=0):
+        per_oc = 1 if groups != 1 else in_channel
+        dense = np.ascontiguousarray(filter, dtype=np.float32).reshape(-1)
+        expect = out_channel * per_oc * kernel_size * kernel_size
+        if dense.size != expect:
+            raise ValueError("filter has %d elements, expected %d" % (dense.size, expect))
+        self._handle = _VP()
+        opts = FilterOpts(oc_block=oc_block, tile_ic=TILE_IC)
+        _check(lib().tetris_filter_create_ex(dense.ctypes.data, in_channel, out_channel, kernel_size,
+                                             groups, device, ctypes.byref(opts),
+                                             ctypes.byref(self._handle)))
+        info = self.info()
+        self.in_channel_, self.out_channel_, self.kernel_size_ = in_channel, out_channel, kernel_size
+        self.groups_ = groups
+        self.nnz_ = info.nnz
+        self.TILE_IC_ = info.tile_ic
+        self.device_ = device
+
+    def info(self):
+        info = FilterInfo()
+        _check(lib().tetris_filter_info(self._handle, ctypes.byref(info)))
+        return info
+
+    def GetTileIC(self):
+        return self.TILE_IC_
+
+    def download(self):
+        """(ops uint64[n_ops], prog_offsets int32[B*T+1]) copied back from the device."""
+        info = self.info()
+        ops = np.empty(info.n_ops, dtype=np.uint64)
+        offs = np.empty(info.n_oc_blocks * info.n_stages + 1, dtype=np.int32)
+        _check(lib().tetris_filter_download(self._handle, ops.ctypes.data, ops.size,
+                                            offs.ctypes.data, offs.size))
+        return ops, offs
+
+    @property
+    def handle(self):
+        if not self._handle:
+            raise RuntimeError("SparseFilter already closed")
+        return self._handle
+
+    def close(self):
+        if getattr(self, "_handle", None):
+            lib().tetris_filter_destroy(self._handle)
+            self._handle = _VP()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def sparse_conv2d(sparse_filter, input, output, batch_size, img_h, img_w, stride, padding,
+                  cuda_stream=None, variant=VARIANT_AUTO):
+    """Launch the convolution: device NHWC `input` -> device NHWC `output`, asynchronous."""
+    _check(lib().tetris_conv2d_launch_ex(sparse_filter.handle, _ptr(input), _ptr(output), batch_size,
+                                         img_h, img_w, stride, padding, _stream_ptr(cuda_stream),
+                                         variant))
+
+
+def timing_sparse_conv2d(sparse_filter, input, output, batch_size, img_h, img_w, stride, padding,
+                         cuda_stream=None, variant=VARIANT_AUTO, warm=WARM, repeat=REPEAT):
+    """Mean milliseconds per launch under the reference's warm-up/repeat protocol."""
+    ms = ctypes.c_float(0.0)
+    _check(lib().tetris_conv2d_time(sparse_filter.handle, _ptr(input), _ptr(output), batch_size,
+                                    img_h, img_w, stride, padding, _stream_ptr(cuda_stream), variant,
+                                    warm, repeat, ctypes.byref(ms)))
+    return ms.value
+
+
+def cuda_sparse_conv2d(h_input, sparse_filter, batch_size, img_h, img_w, stride, padding,
+                       h_output=None, cuda_stream=None):
+    """Host NCHW in, host NCHW out (numpy float32), blocking; returns the output array."""
+    f = sparse_filter
+    oh = out_extent(img_h, f.kernel_size_, stride, padding)
+    ow = out_extent(img_w, f.kernel_size_, stride, padding)
+    h_input = np.ascontiguousarray(h_input, dtype=np.float32)
+    if h_input.size != batch_size * f.in_channel_ * img_h * img_w:
+        raise ValueError("input has %d elements, expected %d"
+                         % (h_input.size, batch_size * f.in_channel_ * img_h * img_w))
+    if h_output is None:
+        h_output = np.empty((batch_size, f.out_channel_, oh, ow), dtype=np.float32)
+    _check(lib().tetris_conv2d_host(f.handle, h_input.ctypes.data, h_output.ctypes.data, batch_size,
+                                    img_h, img_w, stride, padding, _stream_ptr(cuda_stream)))
+    return h_output
+
+
+def cuda_sparse_conv2d_sharded(h_input, sparse_filters, batch_size, img_h, img_w, stride, padding):
+    """As cuda_sparse_conv2d, the batch cut into one contiguous slice per filter/GPU."""
+    f = sparse_filters[0]
+    oh = out_extent(img_h, f.kernel_size_, stride, padding)
+    ow = out_extent(img_w, f.kernel_size_, stride, padding)
+    h_input = np.ascontiguousarray(h_input, dtype=np.float32)
+    h_output = np.empty((batch_size, f.out_channel_, oh, ow), dtype=np.float32)
+    handles = (_VP * len(sparse_filters))(*[sf.handle for sf in sparse_filters])
+    _check(lib().tetris_conv2d_host_sharded(handles, len(sparse_filters), h_input.ctypes.data,
+                                            h_output.ctypes.data, batch_size, img_h, img_w, stride,
+                                            padding))
+    return h_output
+
+
+def nchw_to_nhwc(src, dst, N, C, H, W, cuda_stream=None):
+    _check(lib().tetris_nchw_to_nhwc(_ptr(src), _ptr(dst), N, C, H, W, _stream_ptr(cuda_stream)))
+
+
+def nhwc_to_nchw(src, dst, N, C, H, W, cuda_stream=None):
+    _check(lib().tetris_nhwc_to_nchw(_ptr(src), _ptr(dst), N, C, H, W, _stream_ptr(cuda_stream)))
+
+
+def batch_slice(batch_size, world, rank):
+    """(begin, count) of the contiguous batch slice that shard `rank` of `world` owns."""
+    b, c = ctypes.c_int(0), ctypes.c_int(0)
+    _check(lib().tetris_batch_slice(batch_size, world, rank, ctypes.byref(b), ctypes.byref(c)))
+    return b.value, c.value
+
+
+def device_info(device=0):
+    """(sm_count, sm_clock_khz, fp32_lanes_per_sm)."""
+    a, b, c = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+    _check(lib().tetris_device_info(device, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)))
+    return a.value, b.value, c.value

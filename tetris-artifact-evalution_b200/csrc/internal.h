@@ -1,0 +1,62 @@
+// Internal declarations of the engine: the filter handle, error plumbing and the launchers
+// implemented in the individual .cu files.  Nothing here is part of the C ABI.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/tetris_b200.h"
+#include "format.h"
+
+struct tetris_filter {
+  int in_channel, out_channel, kernel_size, groups;
+  int oc_block, tile_ic;
+  int n_oc_blocks, n_stages;
+  int64_t nnz, n_ops;
+  int device;
+  uint64_t *d_ops;         // program stream (n_ops records incl. tail padding)
+  int32_t *d_prog_offsets; // n_oc_blocks * n_stages + 1 record indices
+  float *d_dense;          // depthwise only: dense [C][KS*KS] filter
+};
+
+namespace tetris {
+
+void set_error(const char *fmt, ...);
+
+#define TETRIS_CUDA_TRY(call)                                                              \
+  do {                                                                                     \
+    cudaError_t err__ = (call);                                                            \
+    if (err__ != cudaSuccess) {                                                            \
+      ::tetris::set_error("%s failed at %s:%d: %s", #call, __FILE__, __LINE__,             \
+                          cudaGetErrorString(err__));                                      \
+      return TETRIS_ERR_CUDA;                                                              \
+    }                                                                                      \
+  } while (0)
+
+struct ConvShape {
+  int N, H, W, IC, OC, KS, S, P, OH, OW;
+};
+
+// compress.cu: dense filter on the device -> program stream.  `d_scratch` holds
+// n_programs + 1 ints (program lengths, then their exclusive scan) and one 64-bit
+// nonzero counter after them.
+size_t compress_scratch_bytes(int n_programs);
+int compress_count(const float *d_filter, int IC, int OC, int KS, int K, int TIC, int B, int T,
+                   int32_t *d_scratch, cudaStream_t st);
+int compress_scan(const int32_t *d_scratch, int32_t *d_offsets, int n_programs, cudaStream_t st);
+const unsigned long long *compress_nnz_ptr(const int32_t *d_scratch, int n_programs);
+int compress_fill(const float *d_filter, int IC, int OC, int KS, int K, int TIC, int B, int T,
+                  const int32_t *d_offsets, uint64_t *d_ops, int64_t n_ops, cudaStream_t st);
+
+// conv_generic.cu / conv_tiled.cu / depthwise.cu / layout.cu
+int launch_conv_generic(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
+                        cudaStream_t st);
+bool conv_tiled_supported(const tetris_filter *f, const ConvShape &s);
+int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
+                      cudaStream_t st);
+int launch_depthwise(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
+                     cudaStream_t st);
+int launch_nchw_to_nhwc(const float *src, float *dst, int N, int C, int H, int W, cudaStream_t st);
+int launch_nhwc_to_nchw(const float *src, float *dst, int N, int C, int H, int W, cudaStream_t st);
+
+}  // namespace tetris
