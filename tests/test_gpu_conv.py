@@ -1,0 +1,180 @@
+"""GPU: convolution parity through the C ABI -- golden vectors, seeded cases, edge cases and
+size-independent properties at full workload size.
+
+Bar: |got - want| <= 1e-4 * max(|got|, |want|) + 1e-5 against the CPU oracle (FP32 with a
+different rounding sequence: the device fuses each multiply-add).
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+VARIANTS = {"auto": 0, "generic": 1, "tiled": 2}
+
+
+def device_conv(tb, torch, f, x_nchw, stride, pad, variant=0, poison=True):
+    """Run the device-pointer entry point: NHWC in, NHWC out; returns NCHW numpy."""
+    n, ic, h, w = x_nchw.shape
+    oh, ow = tb.out_extent(h, f.kernel_size_, stride, pad), tb.out_extent(w, f.kernel_size_, stride, pad)
+    xin = torch.from_numpy(np.ascontiguousarray(x_nchw.transpose(0, 2, 3, 1))).cuda()
+    out = torch.full((n, oh, ow, f.out_channel_), float("nan") if poison else 0.0,
+                     dtype=torch.float32, device="cuda")
+    tb.sparse_conv2d(f, xin, out, n, h, w, stride, pad, variant=variant)
+    torch.cuda.synchronize()
+    return out.cpu().numpy().transpose(0, 3, 1, 2)
+
+
+def tiled_covers(ks, stride):
+    return ks in (1, 3) and stride in (1, 2)
+
+
+def check(oracle, got, want):
+    assert not np.isnan(got).any(), "output elements were left unwritten"
+    bad, max_rel, n_floor = oracle.compare(got, want)
+    assert bad == 0, "%d elements outside 1e-4 (max rel %.3g)" % (bad, max_rel)
+    return max_rel
+
+
+@pytest.mark.parametrize("variant", ["generic", "tiled"])
+@pytest.mark.parametrize("path", GOLDEN, ids=lambda p: os.path.basename(p)[:-4])
+def test_golden_vectors(tb, torch_cuda, oracle, path, variant):
+    z = np.load(path)
+    x, w, stride, pad, want = z["input"], z["filter"], int(z["stride"]), int(z["pad"]), z["output"]
+    oc, ic, ks, _ = w.shape
+    if variant == "tiled" and not tiled_covers(ks, stride):
+        pytest.skip("the tiled kernel covers 1x1 and 3x3 only; auto falls back to generic")
+    f = tb.SparseFilter(w, ic, oc, ks)
+    got = device_conv(tb, torch_cuda, f, x, stride, pad, VARIANTS[variant])
+    check(oracle, got, want)
+    if "all_ones" in path:
+        assert np.array_equal(got, want)  # integer-valued sums are exact in any order
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=lambda p: os.path.basename(p)[:-4])
+def test_golden_vectors_host_entry_point(tb, torch_cuda, oracle, path):
+    """Host NCHW in / host NCHW out, the CudaSparseConv2d-shaped call."""
+    z = np.load(path)
+    x, w, stride, pad, want = z["input"], z["filter"], int(z["stride"]), int(z["pad"]), z["output"]
+    oc, ic, ks, _ = w.shape
+    f = tb.SparseFilter(w, ic, oc, ks)
+    keep = x.copy()
+    got = tb.cuda_sparse_conv2d(x, f, x.shape[0], x.shape[2], x.shape[3], stride, pad)
+    assert np.array_equal(x, keep)
+    check(oracle, got, want)
+
+
+SEEDED = [
+    # N, IC, H, W, OC, KS, stride, pad, density, K, TIC
+    (1, 64, 56, 56, 64, 3, 1, 1, 0.10, 16, 16),    # the single-layer configuration
+    (2, 64, 56, 56, 64, 3, 1, 1, 0.10, 16, 16),    # even batch: image pairs
+    (3, 32, 28, 28, 48, 3, 1, 1, 0.20, 16, 16),    # odd batch > 1
+    (4, 24, 14, 14, 40, 3, 1, 1, 0.15, 16, 8),
+    (2, 16, 7, 7, 32, 3, 1, 1, 0.20, 16, 16),
+    (2, 3, 37, 41, 20, 3, 1, 1, 0.50, 16, 16),     # IC below one stage, ragged H/W
+    (2, 40, 31, 29, 24, 3, 2, 1, 0.15, 16, 16),    # stride 2, odd extents
+    (1, 16, 30, 30, 16, 3, 2, 0, 0.30, 8, 16),
+    (2, 96, 28, 28, 255, 1, 1, 0, 0.20, 16, 32),   # OC not a multiple of anything
+    (2, 384, 13, 13, 128, 1, 1, 0, 0.10, 16, 16),
+    (2, 64, 28, 28, 128, 1, 2, 0, 0.20, 16, 16),   # 1x1 projection, stride 2
+    (1, 35, 9, 200, 18, 3, 1, 1, 0.10, 8, 4),      # very wide and flat
+    (1, 12, 200, 5, 18, 3, 1, 1, 0.10, 16, 16),    # very tall and thin
+    (2, 8, 1, 1, 16, 1, 1, 0, 0.50, 16, 16),       # 1x1 image
+    (2, 8, 2, 3, 16, 3, 1, 1, 0.50, 16, 16),
+]
+
+
+@pytest.mark.parametrize("variant", ["generic", "tiled"])
+@pytest.mark.parametrize("case", SEEDED, ids=lambda c: "n%d_ic%d_%dx%d_oc%d_k%d_s%d_p%d" % c[:8])
+def test_seeded_cases_against_oracle(tb, torch_cuda, oracle, case, variant):
+    n, ic, h, w, oc, ks, stride, pad, density, K, TIC = case
+    rng = np.random.default_rng(hash(case[:8]) % (2 ** 32))
+    filt = rng.normal(0, 0.05, (oc, ic, ks, ks)).astype(np.float32)
+    filt[rng.random(filt.shape) >= density] = 0
+    x = rng.random((n, ic, h, w), dtype=np.float32)
+    x[rng.random(x.shape) < 0.5] = 0
+    f = tb.SparseFilter(filt, ic, oc, ks, TILE_IC=TIC, oc_block=K)
+    got = device_conv(tb, torch_cuda, f, x, stride, pad, VARIANTS[variant])
+    check(oracle, got, oracle.host_conv2d(x, filt, stride, pad))
+
+
+def test_skewed_rows_and_empty_channels(tb, torch_cuda, oracle):
+    """Magnitude-pruned layers have very uneven rows, some with no nonzeros at all."""
+    rng = np.random.default_rng(9)
+    oc, ic = 96, 64
+    filt = rng.normal(0, 0.1, (oc, ic, 3, 3)).astype(np.float32)
+    row_density = rng.beta(0.5, 3.0, oc)
+    row_density[[5, 40, 95]] = 0.0
+    for o in range(oc):
+        filt[o][rng.random(filt[o].shape) >= row_density[o]] = 0
+    x = rng.standard_normal((2, ic, 20, 20)).astype(np.float32)
+    f = tb.SparseFilter(filt, ic, oc, 3)
+    want = oracle.host_conv2d(x, filt, 1, 1)
+    for v in (1, 2):
+        got = device_conv(tb, torch_cuda, f, x, 1, 1, v)
+        check(oracle, got, want)
+        assert np.all(got[:, [5, 40, 95]] == 0)
+
+
+def test_dense_filter_and_negative_inputs(tb, torch_cuda, oracle):
+    rng = np.random.default_rng(10)
+    filt = rng.normal(0, 0.05, (32, 16, 3, 3)).astype(np.float32)
+    x = rng.standard_normal((2, 16, 12, 12)).astype(np.float32)
+    f = tb.SparseFilter(filt, 16, 32, 3)
+    check(oracle, device_conv(tb, torch_cuda, f, x, 1, 1, 2), oracle.host_conv2d(x, filt, 1, 1))
+
+
+def test_empty_batch_and_bad_shapes(tb, torch_cuda):
+    f = tb.SparseFilter(np.ones((16, 8, 3, 3), np.float32), 8, 16, 3)
+    tb.sparse_conv2d(f, None, None, 0, 8, 8, 1, 1)  # empty batch: nothing to do, no error
+    with pytest.raises(tb.TetrisError) as e:
+        tb.sparse_conv2d(f, None, None, 1, 8, 8, 1, 1)
+    assert e.value.status == 1
+    with pytest.raises(tb.TetrisError):
+        tb.sparse_conv2d(f, 1, 1, 1, 2, 2, 1, 0)  # image smaller than the kernel
+    with pytest.raises(tb.TetrisError) as e:
+        f7 = tb.SparseFilter(np.ones((16, 8, 7, 7), np.float32), 8, 16, 7)
+        x = torch_cuda.zeros(1, 8, 8, 8, device="cuda")
+        tb.sparse_conv2d(f7, x, x, 1, 8, 8, 1, 3, variant=2)  # tiled kernel has no 7x7
+    assert e.value.status == 3
+
+
+def test_full_size_properties_vgg_layer(tb, torch_cuda, workloads):
+    """At a full-size layer (VGG conv3_2, batch 16) the CPU oracle is too slow; check
+    properties that hold at any size: the two kernels agree, the op is linear in its input,
+    and a batch is the concatenation of its images."""
+    torch = torch_cuda
+    L = workloads.vgg19()[5]
+    filt = workloads.make_filter("vgg19", 5, L)
+    f = tb.SparseFilter(filt, L.IC, L.OC, L.KS)
+    n = 16
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = torch.rand(n, L.H, L.W, L.IC, device="cuda", generator=g)
+    b = torch.rand(n, L.H, L.W, L.IC, device="cuda", generator=g)
+
+    def run(x, variant, batch=n):
+        out = torch.full((batch, L.H, L.W, L.OC), float("nan"), device="cuda")
+        tb.sparse_conv2d(f, x, out, batch, L.H, L.W, 1, 1, variant=variant)
+        return out
+
+    ya = run(a, 2)
+    assert not torch.isnan(ya).any()
+    yg = run(a, 1)
+    assert torch.allclose(ya, yg, rtol=1e-4, atol=1e-5)
+    lin = run(2.0 * a + b, 2)
+    assert torch.allclose(lin, 2.0 * ya + run(b, 2), rtol=1e-4, atol=1e-4)
+    one = run(a[3:4].contiguous(), 2, batch=1)   # odd batch takes the other pairing mode
+    assert torch.allclose(one[0], ya[3], rtol=1e-5, atol=1e-6)
+
+
+def test_timing_harness_runs(tb, torch_cuda):
+    filt = np.random.default_rng(0).normal(0, 0.05, (64, 64, 3, 3)).astype(np.float32)
+    filt[np.random.default_rng(1).random(filt.shape) < 0.9] = 0
+    f = tb.SparseFilter(filt, 64, 64, 3)
+    x = torch_cuda.rand(1, 56, 56, 64, device="cuda")
+    y = torch_cuda.empty(1, 56, 56, 64, device="cuda")
+    ms = tb.timing_sparse_conv2d(f, x, y, 1, 56, 56, 1, 1, warm=3, repeat=10)
+    assert 0.0 < ms < 50.0

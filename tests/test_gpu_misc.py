@@ -1,0 +1,50 @@
+"""GPU: depthwise convolution, layout transposes and the sharded host entry point."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n,c,h,w,stride", [(2, 32, 20, 20, 1), (1, 64, 15, 17, 2), (3, 7, 5, 4, 1)])
+def test_depthwise_against_oracle(tb, torch_cuda, oracle, n, c, h, w, stride):
+    rng = np.random.default_rng(c)
+    filt = rng.normal(0, 0.05, (c, 1, 3, 3)).astype(np.float32)
+    x = rng.random((n, c, h, w), dtype=np.float32)
+    f = tb.SparseFilter(filt, c, c, 3, groups=c)
+    got = tb.cuda_sparse_conv2d(x, f, n, h, w, stride, 1)
+    bad, max_rel, _ = oracle.compare(got, oracle.host_depthwise_conv2d(x, filt, stride, 1))
+    assert bad == 0, max_rel
+
+
+@pytest.mark.parametrize("shape", [(2, 5, 4, 3), (1, 64, 33, 31), (3, 3, 70, 9), (2, 130, 1, 1)])
+def test_layout_transposes_are_exact(tb, torch_cuda, shape):
+    torch = torch_cuda
+    n, c, h, w = shape
+    x = torch.rand(shape, device="cuda")
+    y = torch.full((n, h, w, c), float("nan"), device="cuda")
+    tb.nchw_to_nhwc(x, y, n, c, h, w)
+    assert torch.equal(y, x.permute(0, 2, 3, 1).contiguous())
+    z = torch.full(shape, float("nan"), device="cuda")
+    tb.nhwc_to_nchw(y, z, n, c, h, w)
+    assert torch.equal(z, x)
+
+
+def test_sharded_host_call_equals_single_call(tb, torch_cuda, oracle):
+    """One filter per shard; with one visible GPU the shards share it, which still exercises
+    the slicing, the worker threads and the per-shard error path."""
+    rng = np.random.default_rng(21)
+    filt = rng.normal(0, 0.05, (32, 16, 3, 3)).astype(np.float32)
+    filt[rng.random(filt.shape) < 0.8] = 0
+    x = rng.random((5, 16, 12, 12), dtype=np.float32)
+    n_dev = torch_cuda.cuda.device_count()
+    shards = 3
+    filters = [tb.SparseFilter(filt, 16, 32, 3, device=g % n_dev) for g in range(shards)]
+    got = tb.cuda_sparse_conv2d_sharded(x, filters, 5, 12, 12, 1, 1)
+    single = tb.cuda_sparse_conv2d(x, filters[0], 5, 12, 12, 1, 1)
+    assert np.array_equal(got, single)
+    assert oracle.compare(got, oracle.host_conv2d(x, filt, 1, 1))[0] == 0
+
+
+def test_device_info(tb, torch_cuda):
+    sms, khz, lanes = tb.device_info(0)
+    assert sms > 0 and khz > 100000 and lanes == 128
