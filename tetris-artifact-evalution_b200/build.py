@@ -41,6 +41,9 @@ def build(force=False, verbose=False):
     """Compile the library if it is missing or older than its sources; returns its path."""
     if not force and not needs_build():
         return LIB
+    sys.path.insert(0, CSRC)
+    import gen_interp  # the PTX interpreter cores are generated, see csrc/gen_interp.py
+    gen_interp.write()
     cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else [])
     cmd += ["-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
     res = subprocess.run(cmd, capture_output=True, text=True)

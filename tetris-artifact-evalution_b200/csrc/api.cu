@@ -3,6 +3,7 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <algorithm>
 #include <new>
 #include <string>
 #include <thread>
@@ -100,8 +101,9 @@ int tetris_filter_create_ex(const float *filter_oihw, int in_channel, int out_ch
     set_error("groups=%d: only 1 or depthwise (groups == ic == oc) is supported", groups);
     return TETRIS_ERR_UNSUPPORTED;
   }
-  int K = opts && opts->oc_block ? opts->oc_block : 16;
-  int TIC = opts && opts->tile_ic ? opts->tile_ic : 16;
+  const int K = opts && opts->oc_block ? opts->oc_block : 16;
+  const bool auto_tic = !(opts && opts->tile_ic);
+  int TIC = auto_tic ? 16 : opts->tile_ic;
   if (!(K == 8 || K == 16) || TIC < 4 || TIC > kMaxTileIc || (TIC & 3)) {
     set_error("bad compression options: oc_block=%d tile_ic=%d", K, TIC);
     return TETRIS_ERR_INVALID;
@@ -153,25 +155,43 @@ int tetris_filter_create_ex(const float *filter_oihw, int in_channel, int out_ch
     return TETRIS_OK;
   }
 
-  const int B = (out_channel + K - 1) / K, T = (in_channel + TIC - 1) / TIC;
-  const int P = B * T;
-  f->n_oc_blocks = B; f->n_stages = T;
-  if (cudaMalloc(&d_scratch, compress_scratch_bytes(P)) != cudaSuccess ||
-      cudaMalloc(&f->d_prog_offsets, (size_t)(P + 1) * sizeof(int32_t)) != cudaSuccess) {
-    cudaGetLastError();
-    set_error("cudaMalloc of compressor scratch failed");
-    return fail(TETRIS_ERR_NOMEM);
-  }
-  if ((rc = compress_count(d_dense, in_channel, out_channel, kernel_size, K, TIC, B, T, d_scratch, 0)) ||
-      (rc = compress_scan(d_scratch, f->d_prog_offsets, P, 0)))
-    return fail(rc);
+  // Programs are staged in shared memory by the tiled kernel, so their length is bounded: when
+  // the stage size is left to the engine, halve it until the longest program is short enough.
+  constexpr int kProgOpsTarget = 640;
+  const int B = (out_channel + K - 1) / K;
+  int T = 0, P = 0;
   int32_t total = 0;
   unsigned long long nnz = 0;
-  if (cudaMemcpy(&total, f->d_prog_offsets + P, sizeof(total), cudaMemcpyDeviceToHost) != cudaSuccess ||
-      cudaMemcpy(&nnz, compress_nnz_ptr(d_scratch, P), sizeof(nnz), cudaMemcpyDeviceToHost) != cudaSuccess) {
-    set_error("compressor count/scan failed: %s", cudaGetErrorString(cudaGetLastError()));
-    return fail(TETRIS_ERR_CUDA);
+  std::vector<int32_t> h_offsets;
+  for (;;) {
+    T = (in_channel + TIC - 1) / TIC;
+    P = B * T;
+    cudaFree(d_scratch); cudaFree(f->d_prog_offsets);
+    d_scratch = nullptr; f->d_prog_offsets = nullptr;
+    if (cudaMalloc(&d_scratch, compress_scratch_bytes(P)) != cudaSuccess ||
+        cudaMalloc(&f->d_prog_offsets, (size_t)(P + 1) * sizeof(int32_t)) != cudaSuccess) {
+      cudaGetLastError();
+      set_error("cudaMalloc of compressor scratch failed");
+      return fail(TETRIS_ERR_NOMEM);
+    }
+    if ((rc = compress_count(d_dense, in_channel, out_channel, kernel_size, K, TIC, B, T, d_scratch, 0)) ||
+        (rc = compress_scan(d_scratch, f->d_prog_offsets, P, 0)))
+      return fail(rc);
+    h_offsets.resize(P + 1);
+    if (cudaMemcpy(h_offsets.data(), f->d_prog_offsets, (size_t)(P + 1) * sizeof(int32_t), cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(&nnz, compress_nnz_ptr(d_scratch, P), sizeof(nnz), cudaMemcpyDeviceToHost) != cudaSuccess) {
+      set_error("compressor count/scan failed: %s", cudaGetErrorString(cudaGetLastError()));
+      return fail(TETRIS_ERR_CUDA);
+    }
+    total = h_offsets[P];
+    int longest = 0;
+    for (int i = 0; i < P; ++i) longest = std::max(longest, h_offsets[i + 1] - h_offsets[i]);
+    f->max_prog_ops = longest;
+    if (!auto_tic || longest <= kProgOpsTarget || TIC <= 4) break;
+    TIC /= 2;
   }
+  f->tile_ic = TIC;
+  f->n_oc_blocks = B; f->n_stages = T;
   f->nnz = (int64_t)nnz;
   f->n_ops = (int64_t)total + kTailPadOps;
   if (cudaMalloc(&f->d_ops, (size_t)f->n_ops * sizeof(uint64_t)) != cudaSuccess) {

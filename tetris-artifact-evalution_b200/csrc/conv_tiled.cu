@@ -26,6 +26,7 @@
 // NHWC in, NHWC out, FP32, output fully overwritten -- the contract of the reference launcher
 // (Tetris/spconv2d_kernel.cu:163-188).
 #include "internal.h"
+#include "interp_gen.h"
 
 namespace tetris {
 namespace {
@@ -46,7 +47,7 @@ struct WinCfg {
 struct TiledParams {
   const float *in;
   float *out;
-  const uint4 *ops;
+  const uint2 *ops;
   const int32_t *prog_offsets;
   int N, H, W, IC, OC, OH, OW, P;
   int TS, TH;            // segments per tile row, tile rows; TS*TH lanes are in use
@@ -58,19 +59,16 @@ struct TiledParams {
   int icpitch;           // bytes per channel slab
   int stage_bytes;       // TIC * icpitch
   int n_entries;         // staging table entries: 2*ROWS*CIN2
+  int prog_bytes;        // shared bytes reserved per warp and buffer for its staged program
   int T, B, TIC, tic_shift;
 };
 
-__device__ __forceinline__ float4 lds128(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(addr));
-  return v;
-}
 __device__ __forceinline__ void cp_async4(uint32_t dst, const float *src, int src_bytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
                : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -78,83 +76,15 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// ---- the interpreter's jump-table cases -------------------------------------------------------
-#define T_FMA(k, s)                                                               \
-  {                                                                               \
-    _Pragma("unroll") for (int p = 0; p < P2; ++p) acc[(k)][p] =                  \
-        __ffma2_rn(w2, xw[p * S + (s)], acc[(k)][p]);                             \
-  }
-#define T_CASE1(k) case (k): T_FMA(k, 0) break;
-#define T_CASE3(k)                 \
-  case 3 * (k): T_FMA(k, 0) break; \
-  case 3 * (k) + 1: T_FMA(k, 1) break; \
-  case 3 * (k) + 2: T_FMA(k, 2) break;
-#define T_REP8(M) M(0) M(1) M(2) M(3) M(4) M(5) M(6) M(7)
-#define T_REP16(M) T_REP8(M) M(8) M(9) M(10) M(11) M(12) M(13) M(14) M(15)
-
-#define T_LOADX(lo)                                                                        \
-  {                                                                                        \
-    const uint32_t a_ic = sbase + ((lo) >> 8) * (uint32_t)p.icpitch;                       \
-    const uint32_t r_ = (lo)&255u;                                                         \
-    const uint32_t a_own = a_ic + own_base + r_ * rp;                                      \
-    _Pragma("unroll") for (int j = 0; j < C::OWN; ++j) {                                   \
-      const float4 c = lds128(a_own + j * (uint32_t)p.cp16);                               \
-      xw[2 * j] = make_float2(c.x, c.y);                                                   \
-      xw[2 * j + 1] = make_float2(c.z, c.w);                                               \
-    }                                                                                      \
-    if constexpr (C::HALO > 0) {                                                           \
-      const uint32_t a_h = a_ic + halo_base + r_ * halo_rp;                                \
-      _Pragma("unroll") for (int j = 0; j < C::HALO; ++j) {                                \
-        const float4 c = lds128(a_h + j * halo_js);                                        \
-        xw[2 * (C::OWN + j)] = make_float2(c.x, c.y);                                      \
-        xw[2 * (C::OWN + j) + 1] = make_float2(c.z, c.w);                                  \
-      }                                                                                    \
-    }                                                                                      \
-  }
-
-#define T_DISPATCH(lo, hi)                                              \
-  {                                                                     \
-    const float wv = __uint_as_float(lo);                               \
-    const float2 w2 = make_float2(wv, wv);                              \
-    if constexpr (KS == 3 && K == 16) {                                 \
-      switch (hi) {                                                     \
-        T_REP16(T_CASE3)                                                \
-        case 48: T_LOADX(lo) break;                                     \
-        case 49: goto program_done;                                     \
-        default: __builtin_unreachable();                               \
-      }                                                                 \
-    } else if constexpr (KS == 3 && K == 8) {                           \
-      switch (hi) {                                                     \
-        T_REP8(T_CASE3)                                                 \
-        case 24: T_LOADX(lo) break;                                     \
-        case 25: goto program_done;                                     \
-        default: __builtin_unreachable();                               \
-      }                                                                 \
-    } else if constexpr (KS == 1 && K == 16) {                          \
-      switch (hi) {                                                     \
-        T_REP16(T_CASE1)                                                \
-        case 16: T_LOADX(lo) break;                                     \
-        case 17: goto program_done;                                     \
-        default: __builtin_unreachable();                               \
-      }                                                                 \
-    } else {                                                            \
-      static_assert(KS == 1 && K == 8, "unsupported (KS, K)");          \
-      switch (hi) {                                                     \
-        T_REP8(T_CASE1)                                                 \
-        case 8: T_LOADX(lo) break;                                      \
-        case 9: goto program_done;                                      \
-        default: __builtin_unreachable();                               \
-      }                                                                 \
-    }                                                                   \
-  }
-
 template <int KS, int S, int K, int P2, int MINB>
 __global__ void __launch_bounds__(kWarps * 32, MINB) conv_tiled_kernel(const TiledParams p) {
   using C = WinCfg<KS, S, P2>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(smem_raw);
-  // layout: [stage buffer 0][stage buffer 1][staging table: n_entries x {goff, soff}]
-  int2 *tab = reinterpret_cast<int2 *>(smem_raw + 2 * p.stage_bytes);
+  // layout: [input tile 0][input tile 1][programs 0: kWarps x prog_bytes][programs 1]
+  //         [staging table: n_entries x {goff, soff}]
+  const uint32_t prog0 = smem0 + 2 * p.stage_bytes;
+  int2 *tab = reinterpret_cast<int2 *>(smem_raw + 2 * p.stage_bytes + 2 * kWarps * p.prog_bytes);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
@@ -191,9 +121,18 @@ __global__ void __launch_bounds__(kWarps * 32, MINB) conv_tiled_kernel(const Til
   }
   __syncthreads();
 
+  const int b = blockIdx.y * kWarps + warp;  // output-channel block of this warp
+  const bool warp_on = b < p.B;
+
   const int icl_s = tid & (p.TIC - 1);  // this thread's channel inside a stage (staging role)
   const int pe0 = tid >> p.tic_shift, pe_step = (kWarps * 32) >> p.tic_shift;
-  auto issue_stage = [&](int t, uint32_t dst_base) {
+  auto issue_stage = [&](int t, int buf) {
+    const uint32_t dst_base = smem0 + buf * p.stage_bytes;
+    if (warp_on) {  // this warp's program of the stage, 16 bytes (two records) per copy
+      const int po = p.prog_offsets[b * p.T + t], pn = p.prog_offsets[b * p.T + t + 1];
+      const uint32_t dst_p = prog0 + (buf * kWarps + warp) * p.prog_bytes;
+      for (int i = lane; 2 * i < pn - po; i += 32) cp_async16(dst_p + i * 16, p.ops + po + 2 * i);
+    }
     const int ic = t * p.TIC + icl_s;
     if (ic < p.IC) {
       const float *src_c = p.in + ic;
@@ -220,22 +159,14 @@ __global__ void __launch_bounds__(kWarps * 32, MINB) conv_tiled_kernel(const Til
     halo_js = inner ? (uint32_t)p.cp16 : 16u;
   }
 
-  const int b = blockIdx.y * kWarps + warp;  // output-channel block of this warp
-  const bool warp_on = b < p.B;
+  using I = Interp<KS, S, K, P2>;
+  I::init();  // K*P2 packed accumulators, zeroed, in registers the interpreter names statically
 
-  float2 acc[K][P2];
-#pragma unroll
-  for (int k = 0; k < K; ++k)
-#pragma unroll
-    for (int q = 0; q < P2; ++q) acc[k][q] = make_float2(0.f, 0.f);
-  float2 xw[2 * C::NCH];
-#pragma unroll
-  for (int q = 0; q < 2 * C::NCH; ++q) xw[q] = make_float2(0.f, 0.f);
-
-  issue_stage(0, smem0);
+  issue_stage(0, 0);
+#pragma unroll 1
   for (int t = 0; t < p.T; ++t) {
     if (t + 1 < p.T) {
-      issue_stage(t + 1, smem0 + ((t + 1) & 1) * p.stage_bytes);
+      issue_stage(t + 1, (t + 1) & 1);
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
@@ -243,26 +174,15 @@ __global__ void __launch_bounds__(kWarps * 32, MINB) conv_tiled_kernel(const Til
     __syncthreads();
     if (warp_on) {
       const uint32_t sbase = smem0 + (t & 1) * p.stage_bytes;
-      const uint4 *pc = p.ops + (p.prog_offsets[b * p.T + t] >> 1);
-      uint4 q0 = __ldg(pc), q1 = __ldg(pc + 1);
-      pc += 2;
-#pragma unroll 1
-      for (;;) {
-        const uint4 n0q = __ldg(pc), n1q = __ldg(pc + 1);
-        pc += 2;
-        T_DISPATCH(q0.x, q0.y)
-        T_DISPATCH(q0.z, q0.w)
-        T_DISPATCH(q1.x, q1.y)
-        T_DISPATCH(q1.z, q1.w)
-        q0 = n0q;
-        q1 = n1q;
-      }
-    program_done:;
+      I::run(prog0 + ((t & 1) * kWarps + warp) * p.prog_bytes, sbase + own_base, sbase + halo_base,
+             (uint32_t)p.icpitch, rp, halo_rp, (uint32_t)p.cp16, halo_js);
     }
     __syncthreads();
   }
 
   // ---- epilogue: NHWC stores, K consecutive channels per pixel ----
+  float2 acc[K][P2];
+  I::read(acc);
   if (!warp_on || !lane_on) return;
   const int oc0 = b * K;
   const int kn = min(K, p.OC - oc0);
@@ -304,7 +224,7 @@ struct Geometry {
 };
 
 template <int KS, int S, int P2>
-bool choose_geometry(const ConvShape &s, int TIC, size_t smem_limit, Geometry *g) {
+bool choose_geometry(const ConvShape &s, int TIC, size_t smem_limit, size_t prog_total, Geometry *g) {
   using C = WinCfg<KS, S, P2>;
   const int pair_mode = (s.N % 2 == 0) ? 0 : 1;
   double best = 1e300;
@@ -319,7 +239,7 @@ bool choose_geometry(const ConvShape &s, int TIC, size_t smem_limit, Geometry *g
       int icpitch = (C::OWN * ROWS * TS + ROWS * C::HALO) * 16;
       if (((icpitch / 16) & 1) == 0) icpitch += 16;  // odd chunk pitch: fewer staging conflicts
       const int n_entries = 2 * ROWS * CIN2;
-      const size_t smem = 2 * (size_t)TIC * icpitch + (size_t)n_entries * sizeof(int2);
+      const size_t smem = 2 * (size_t)TIC * icpitch + (size_t)n_entries * sizeof(int2) + prog_total;
       if (smem > smem_limit) continue;
       // cost model: every tile runs one full warp program per stage whatever its lane use;
       // staging grows with the staged area.
@@ -347,13 +267,15 @@ int launch_instance(const tetris_filter *f, const float *in, float *out, const C
                     cudaStream_t st) {
   Geometry g;
   const size_t smem_limit = 200 * 1024 / MINB;
-  if (!choose_geometry<KS, S, P2>(s, f->tile_ic, smem_limit, &g)) {
+  // one record of slack: the interpreter prefetches one record past END
+  const int prog_bytes = ((f->max_prog_ops + 2) * 8 + 15) / 16 * 16;
+  if (!choose_geometry<KS, S, P2>(s, f->tile_ic, smem_limit, (size_t)2 * kWarps * prog_bytes, &g)) {
     set_error("tiled kernel: no tile geometry fits shared memory");
     return TETRIS_ERR_UNSUPPORTED;
   }
   TiledParams p;
   p.in = in; p.out = out;
-  p.ops = reinterpret_cast<const uint4 *>(f->d_ops);
+  p.ops = reinterpret_cast<const uint2 *>(f->d_ops);
   p.prog_offsets = f->d_prog_offsets;
   p.N = s.N; p.H = s.H; p.W = s.W; p.IC = s.IC; p.OC = s.OC; p.OH = s.OH; p.OW = s.OW; p.P = s.P;
   p.TS = g.TS; p.TH = g.TH; p.tiles_w = g.tiles_w; p.tiles_h = g.tiles_h;
@@ -361,6 +283,7 @@ int launch_instance(const tetris_filter *f, const float *in, float *out, const C
   p.ROWS = g.ROWS; p.CIN2 = g.CIN2; p.cp16 = g.cp16; p.hbase = g.hbase; p.icpitch = g.icpitch;
   p.stage_bytes = f->tile_ic * g.icpitch;
   p.n_entries = g.n_entries;
+  p.prog_bytes = prog_bytes;
   p.T = f->n_stages; p.B = f->n_oc_blocks; p.TIC = f->tile_ic;
   p.tic_shift = 0;
   while ((1 << p.tic_shift) < f->tile_ic) ++p.tic_shift;

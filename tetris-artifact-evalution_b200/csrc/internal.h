@@ -13,6 +13,7 @@ struct tetris_filter {
   int oc_block, tile_ic;
   int n_oc_blocks, n_stages;
   int64_t nnz, n_ops;
+  int max_prog_ops;        // longest program, in records
   int device;
   uint64_t *d_ops;         // program stream (n_ops records incl. tail padding)
   int32_t *d_prog_offsets; // n_oc_blocks * n_stages + 1 record indices
