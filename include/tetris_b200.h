@@ -11,7 +11,8 @@
  *                             reorder + upload, Tetris/spconv2d_utils.h:25-265
  *   tetris_filter_destroy     ~SparseFilter, Tetris/spconv2d_utils.h:267-273
  *   tetris_filter_info/
- *   tetris_filter_download    the public fields and Get*() getters,
+ *   tetris_filter_download/
+ *   tetris_filter_download_lists  the public fields and Get*() getters,
  *                             Tetris/spconv2d_utils.h:495-514
  *   tetris_conv2d_launch      SparseConv2d<...>() launcher,
  *                             Tetris/spconv2d_kernel.cu:163-188
@@ -47,7 +48,9 @@ enum {
 enum {
   TETRIS_VARIANT_AUTO = 0,    /* fastest kernel that covers the shape              */
   TETRIS_VARIANT_GENERIC = 1, /* one thread per output pixel, any KS/stride        */
-  TETRIS_VARIANT_TILED = 2    /* shared-memory tile + register-blocked interpreter */
+  TETRIS_VARIANT_TILED = 2,   /* shared-memory tile, per-channel weight lists          */
+  TETRIS_VARIANT_INTERP = 3   /* shared-memory tile, jump-table interpreter that reuses a
+                                 register-resident input window across channels (1x1, 3x3) */
 };
 
 typedef struct tetris_filter tetris_filter_t; /* opaque; owns device buffers */
@@ -66,9 +69,10 @@ typedef struct {
   int n_stages;           /* ceil(in_channel / tile_ic)                            */
   int64_t nnz;            /* nonzero weights, padding excluded                     */
   int64_t n_ops;          /* 8-byte records in the compressed program stream       */
-  int64_t compressed_bytes; /* device bytes held: ops + program offsets            */
+  int64_t compressed_bytes; /* device bytes held by both compressed forms          */
+  int64_t n_list_units;   /* 8-byte units in the list form                         */
   int device;
-  int reserved[7];
+  int reserved[5];
 } tetris_filter_info_t;
 
 /*
@@ -87,12 +91,16 @@ void tetris_filter_destroy(tetris_filter_t *f);
 int tetris_filter_info(const tetris_filter_t *f, tetris_filter_info_t *info);
 
 /*
- * Copy the compressed form back to the host: `ops` receives n_ops 8-byte
+ * Copy the compressed program form back to the host: `ops` receives n_ops 8-byte
  * records, `prog_offsets` receives n_oc_blocks * n_stages + 1 record indices.
  * Either pointer may be NULL to skip that array.
  */
 int tetris_filter_download(const tetris_filter_t *f, uint64_t *ops, size_t ops_capacity,
                            int32_t *prog_offsets, size_t offsets_capacity);
+
+/* The same for the list form: n_list_units 8-byte units and the per-piece unit offsets. */
+int tetris_filter_download_lists(const tetris_filter_t *f, uint64_t *units, size_t units_capacity,
+                                 int32_t *list_offsets, size_t offsets_capacity);
 
 /*
  * Convolution, device pointers, NHWC in and NHWC out as in the reference

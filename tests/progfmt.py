@@ -62,3 +62,57 @@ def unpack(ops, offsets, OC, IC, KS, K=16, TIC=16):
                 k, s = divmod(code, KS)
                 w[b * K + k, ic, r, s] = payload
     return w.view(np.float32)
+
+
+LIST_HEADER_WORDS = 4
+LIST_TAIL_UNITS = 2
+
+
+def pack_lists(w, K=16, TIC=16):
+    """Dense OIHW float32 -> (units uint64[], piece_offsets int32[B*T+1]) of the LIST form:
+    per piece K counts + total + 3 zero words, then the K lists of {weight, pos} records in
+    (ic, r, s) order, then a zero sentinel; pieces padded to an even number of 8-byte units."""
+    w = np.ascontiguousarray(w, np.float32)
+    OC, IC, KS, _ = w.shape
+    B, T = -(-OC // K), -(-IC // TIC)
+    bits = w.view(np.uint32)
+    words, offsets = [], [0]           # 32-bit words; two per unit
+    for b in range(B):
+        for t in range(T):
+            start = len(words)
+            counts, recs = [], []
+            for k in range(K):
+                oc = b * K + k
+                n = 0
+                if oc < OC:
+                    blk = w[oc, t * TIC:(t + 1) * TIC]           # [icl][r][s]
+                    for icl, r, s in zip(*np.nonzero(blk != 0)):  # row-major = (ic, r, s) order
+                        recs += [int(bits[oc, t * TIC + icl, r, s]), (int(icl) << 8) | (int(r) << 4) | int(s)]
+                        n += 1
+                counts.append(n)
+            words += counts + [sum(counts), 0, 0, 0] + recs + [0, 0]
+            while ((len(words) - start) // 2) % PROG_ALIGN_OPS:
+                words += [0, 0]
+            offsets.append(len(words) // 2)
+    words += [0, 0] * LIST_TAIL_UNITS
+    return np.array(words, np.uint32).view(np.uint64), np.array(offsets, np.int32)
+
+
+def unpack_lists(units, offsets, OC, IC, KS, K=16, TIC=16):
+    """LIST form -> dense OIHW float32."""
+    B, T = -(-OC // K), -(-IC // TIC)
+    words = np.ascontiguousarray(units).view(np.uint32)
+    w = np.zeros((OC, IC, KS, KS), np.uint32)
+    for b in range(B):
+        for t in range(T):
+            base = 2 * int(offsets[b * T + t])
+            counts = words[base:base + K]
+            assert int(words[base + K]) == int(counts.sum())
+            i = base + K + LIST_HEADER_WORDS
+            for k in range(K):
+                for _ in range(int(counts[k])):
+                    val, pos = int(words[i]), int(words[i + 1])
+                    i += 2
+                    w[b * K + k, t * TIC + (pos >> 8), (pos >> 4) & 15, pos & 15] = val
+            assert words[i] == 0 and words[i + 1] == 0  # the sentinel
+    return w.view(np.float32)

@@ -39,6 +39,10 @@ def test_stream_is_bit_identical_to_the_packer(tb, torch_cuda, OC, IC, KS, densi
     assert (info.n_oc_blocks, info.n_stages) == (-(-OC // K), -(-IC // TIC))
     assert np.array_equal(offs, want_offs)
     assert np.array_equal(ops, want_ops)
+    units, loffs = f.download_lists()
+    want_units, want_loffs = progfmt.pack_lists(w, K, TIC)
+    assert np.array_equal(loffs, want_loffs)
+    assert np.array_equal(units, want_units)
     f.close()
 
 
@@ -50,6 +54,10 @@ def test_compress_then_decompress_returns_the_filter(tb, torch_cuda, OC, IC, KS,
     ops, offs = f.download()
     back = progfmt.unpack(ops, offs, OC, IC, KS, K, TIC)
     assert np.array_equal(back, w)  # value equality: -0.0 == 0.0
+    assert np.array_equal(back.view(np.uint32)[w != 0], w.view(np.uint32)[w != 0])
+    units, loffs = f.download_lists()
+    back = progfmt.unpack_lists(units, loffs, OC, IC, KS, K, TIC)
+    assert np.array_equal(back, w)
     assert np.array_equal(back.view(np.uint32)[w != 0], w.view(np.uint32)[w != 0])
 
 

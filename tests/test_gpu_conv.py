@@ -13,7 +13,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
-VARIANTS = {"auto": 0, "generic": 1, "tiled": 2}
+VARIANTS = {"auto": 0, "generic": 1, "tiled": 2, "interp": 3}
 
 
 def device_conv(tb, torch, f, x_nchw, stride, pad, variant=0, poison=True):
@@ -28,8 +28,9 @@ def device_conv(tb, torch, f, x_nchw, stride, pad, variant=0, poison=True):
     return out.cpu().numpy().transpose(0, 3, 1, 2)
 
 
-def tiled_covers(ks, stride):
-    return ks in (1, 3) and stride in (1, 2)
+def covers(variant, ks, stride):
+    """The interpreter kernel is instantiated for 1x1 and 3x3, stride 1 and 2 only."""
+    return variant != "interp" or (ks in (1, 3) and stride in (1, 2))
 
 
 def check(oracle, got, want):
@@ -39,14 +40,14 @@ def check(oracle, got, want):
     return max_rel
 
 
-@pytest.mark.parametrize("variant", ["generic", "tiled"])
+@pytest.mark.parametrize("variant", ["generic", "tiled", "interp"])
 @pytest.mark.parametrize("path", GOLDEN, ids=lambda p: os.path.basename(p)[:-4])
 def test_golden_vectors(tb, torch_cuda, oracle, path, variant):
     z = np.load(path)
     x, w, stride, pad, want = z["input"], z["filter"], int(z["stride"]), int(z["pad"]), z["output"]
     oc, ic, ks, _ = w.shape
-    if variant == "tiled" and not tiled_covers(ks, stride):
-        pytest.skip("the tiled kernel covers 1x1 and 3x3 only; auto falls back to generic")
+    if not covers(variant, ks, stride):
+        pytest.skip("the interpreter kernel covers 1x1 and 3x3 only")
     f = tb.SparseFilter(w, ic, oc, ks)
     got = device_conv(tb, torch_cuda, f, x, stride, pad, VARIANTS[variant])
     check(oracle, got, want)
@@ -84,10 +85,12 @@ SEEDED = [
     (1, 12, 200, 5, 18, 3, 1, 1, 0.10, 16, 16),    # very tall and thin
     (2, 8, 1, 1, 16, 1, 1, 0, 0.50, 16, 16),       # 1x1 image
     (2, 8, 2, 3, 16, 3, 1, 1, 0.50, 16, 16),
+    (2, 3, 40, 36, 24, 7, 2, 3, 0.50, 16, 16),     # the 7x7 stride-2 stem shape
+    (1, 6, 21, 19, 10, 5, 3, 2, 0.40, 8, 4),       # 5x5, stride 3
 ]
 
 
-@pytest.mark.parametrize("variant", ["generic", "tiled"])
+@pytest.mark.parametrize("variant", ["generic", "tiled", "interp"])
 @pytest.mark.parametrize("case", SEEDED, ids=lambda c: "n%d_ic%d_%dx%d_oc%d_k%d_s%d_p%d" % c[:8])
 def test_seeded_cases_against_oracle(tb, torch_cuda, oracle, case, variant):
     n, ic, h, w, oc, ks, stride, pad, density, K, TIC = case
@@ -96,6 +99,8 @@ def test_seeded_cases_against_oracle(tb, torch_cuda, oracle, case, variant):
     filt[rng.random(filt.shape) >= density] = 0
     x = rng.random((n, ic, h, w), dtype=np.float32)
     x[rng.random(x.shape) < 0.5] = 0
+    if not covers(variant, ks, stride):
+        pytest.skip("the interpreter kernel covers 1x1 and 3x3 only")
     f = tb.SparseFilter(filt, ic, oc, ks, TILE_IC=TIC, oc_block=K)
     got = device_conv(tb, torch_cuda, f, x, stride, pad, VARIANTS[variant])
     check(oracle, got, oracle.host_conv2d(x, filt, stride, pad))
@@ -113,7 +118,7 @@ def test_skewed_rows_and_empty_channels(tb, torch_cuda, oracle):
     x = rng.standard_normal((2, ic, 20, 20)).astype(np.float32)
     f = tb.SparseFilter(filt, ic, oc, 3)
     want = oracle.host_conv2d(x, filt, 1, 1)
-    for v in (1, 2):
+    for v in (1, 2, 3):
         got = device_conv(tb, torch_cuda, f, x, 1, 1, v)
         check(oracle, got, want)
         assert np.all(got[:, [5, 40, 95]] == 0)
@@ -138,7 +143,7 @@ def test_empty_batch_and_bad_shapes(tb, torch_cuda):
     with pytest.raises(tb.TetrisError) as e:
         f7 = tb.SparseFilter(np.ones((16, 8, 7, 7), np.float32), 8, 16, 7)
         x = torch_cuda.zeros(1, 8, 8, 8, device="cuda")
-        tb.sparse_conv2d(f7, x, x, 1, 8, 8, 1, 3, variant=2)  # tiled kernel has no 7x7
+        tb.sparse_conv2d(f7, x, x, 1, 8, 8, 1, 3, variant=3)  # the interpreter has no 7x7
     assert e.value.status == 3
 
 
@@ -164,6 +169,7 @@ def test_full_size_properties_vgg_layer(tb, torch_cuda, workloads):
     assert not torch.isnan(ya).any()
     yg = run(a, 1)
     assert torch.allclose(ya, yg, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(ya, run(a, 3), rtol=1e-4, atol=1e-5)
     lin = run(2.0 * a + b, 2)
     assert torch.allclose(lin, 2.0 * ya + run(b, 2), rtol=1e-4, atol=1e-4)
     one = run(a[3:4].contiguous(), 2, batch=1)   # odd batch takes the other pairing mode

@@ -31,7 +31,7 @@ LIB_PATH = os.path.join(_HERE, "libtetris_b200.so")
 WARM = 30     # Tetris/tensor_utils.h:11
 REPEAT = 100  # Tetris/tensor_utils.h:10
 
-VARIANT_AUTO, VARIANT_GENERIC, VARIANT_TILED = 0, 1, 2
+VARIANT_AUTO, VARIANT_GENERIC, VARIANT_TILED, VARIANT_INTERP = 0, 1, 2, 3
 
 _c_float_p = ctypes.POINTER(ctypes.c_float)
 _c_int_p = ctypes.POINTER(ctypes.c_int)
@@ -48,7 +48,8 @@ class FilterInfo(ctypes.Structure):
         ("oc_block", ctypes.c_int), ("tile_ic", ctypes.c_int),
         ("n_oc_blocks", ctypes.c_int), ("n_stages", ctypes.c_int),
         ("nnz", ctypes.c_int64), ("n_ops", ctypes.c_int64), ("compressed_bytes", ctypes.c_int64),
-        ("device", ctypes.c_int), ("reserved", ctypes.c_int * 7),
+        ("n_list_units", ctypes.c_int64),
+        ("device", ctypes.c_int), ("reserved", ctypes.c_int * 5),
     ]
 
 
@@ -61,6 +62,7 @@ SIGNATURES = {
     "tetris_filter_destroy": (None, [_VP]),
     "tetris_filter_info": (_I, [_VP, ctypes.POINTER(FilterInfo)]),
     "tetris_filter_download": (_I, [_VP, _VP, ctypes.c_size_t, _VP, ctypes.c_size_t]),
+    "tetris_filter_download_lists": (_I, [_VP, _VP, ctypes.c_size_t, _VP, ctypes.c_size_t]),
     "tetris_conv2d_launch": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
     "tetris_conv2d_launch_ex": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I]),
     "tetris_conv2d_time": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _I, _I, _c_float_p]),
@@ -176,6 +178,15 @@ class SparseFilter:
         _check(lib().tetris_filter_download(self._handle, ops.ctypes.data, ops.size,
                                             offs.ctypes.data, offs.size))
         return ops, offs
+
+    def download_lists(self):
+        """(units uint64[n_list_units], list_offsets int32[B*T+1]) of the list form."""
+        info = self.info()
+        units = np.empty(info.n_list_units, dtype=np.uint64)
+        offs = np.empty(info.n_oc_blocks * info.n_stages + 1, dtype=np.int32)
+        _check(lib().tetris_filter_download_lists(self._handle, units.ctypes.data, units.size,
+                                                  offs.ctypes.data, offs.size))
+        return units, offs
 
     @property
     def handle(self):

@@ -64,6 +64,7 @@ int dispatch(const tetris_filter *f, const float *in, float *out, const ConvShap
   switch (variant) {
     case TETRIS_VARIANT_GENERIC: return launch_conv_generic(f, in, out, s, st);
     case TETRIS_VARIANT_TILED: return launch_conv_tiled(f, in, out, s, st);
+    case TETRIS_VARIANT_INTERP: return launch_conv_interp(f, in, out, s, st);
     case TETRIS_VARIANT_AUTO:
       return conv_tiled_supported(f, s) ? launch_conv_tiled(f, in, out, s, st)
                                         : launch_conv_generic(f, in, out, s, st);
@@ -155,43 +156,73 @@ int tetris_filter_create_ex(const float *filter_oihw, int in_channel, int out_ch
     return TETRIS_OK;
   }
 
-  // Programs are staged in shared memory by the tiled kernel, so their length is bounded: when
-  // the stage size is left to the engine, halve it until the longest program is short enough.
-  constexpr int kProgOpsTarget = 640;
+  // List pieces are staged in shared memory by the tiled kernel, so their length is bounded:
+  // when the stage size is left to the engine, halve it until the longest piece is short enough.
+  constexpr int kPieceUnitsTarget = 640;
   const int B = (out_channel + K - 1) / K;
   int T = 0, P = 0;
-  int32_t total = 0;
-  unsigned long long nnz = 0;
   std::vector<int32_t> h_offsets;
+  auto alloc_offsets = [&](int32_t **d_offsets) {
+    cudaFree(d_scratch); cudaFree(*d_offsets);
+    d_scratch = nullptr; *d_offsets = nullptr;
+    return cudaMalloc(&d_scratch, compress_scratch_bytes(P)) == cudaSuccess &&
+           cudaMalloc(d_offsets, (size_t)(P + 1) * sizeof(int32_t)) == cudaSuccess;
+  };
+  auto fetch_offsets = [&](const int32_t *d_offsets, int *longest) {
+    h_offsets.resize(P + 1);
+    if (cudaMemcpy(h_offsets.data(), d_offsets, (size_t)(P + 1) * sizeof(int32_t),
+                   cudaMemcpyDeviceToHost) != cudaSuccess)
+      return false;
+    *longest = 0;
+    for (int i = 0; i < P; ++i) *longest = std::max(*longest, h_offsets[i + 1] - h_offsets[i]);
+    return true;
+  };
+  // ---- LIST form (tiled kernel) ----
   for (;;) {
     T = (in_channel + TIC - 1) / TIC;
     P = B * T;
-    cudaFree(d_scratch); cudaFree(f->d_prog_offsets);
-    d_scratch = nullptr; f->d_prog_offsets = nullptr;
-    if (cudaMalloc(&d_scratch, compress_scratch_bytes(P)) != cudaSuccess ||
-        cudaMalloc(&f->d_prog_offsets, (size_t)(P + 1) * sizeof(int32_t)) != cudaSuccess) {
+    if (!alloc_offsets(&f->d_list_offsets)) {
       cudaGetLastError();
       set_error("cudaMalloc of compressor scratch failed");
       return fail(TETRIS_ERR_NOMEM);
     }
-    if ((rc = compress_count(d_dense, in_channel, out_channel, kernel_size, K, TIC, B, T, d_scratch, 0)) ||
-        (rc = compress_scan(d_scratch, f->d_prog_offsets, P, 0)))
+    if ((rc = list_count(d_dense, in_channel, out_channel, kernel_size, K, TIC, B, T, d_scratch, 0)) ||
+        (rc = compress_scan(d_scratch, f->d_list_offsets, P, 0)))
       return fail(rc);
-    h_offsets.resize(P + 1);
-    if (cudaMemcpy(h_offsets.data(), f->d_prog_offsets, (size_t)(P + 1) * sizeof(int32_t), cudaMemcpyDeviceToHost) != cudaSuccess ||
-        cudaMemcpy(&nnz, compress_nnz_ptr(d_scratch, P), sizeof(nnz), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    if (!fetch_offsets(f->d_list_offsets, &f->max_list_units)) {
       set_error("compressor count/scan failed: %s", cudaGetErrorString(cudaGetLastError()));
       return fail(TETRIS_ERR_CUDA);
     }
-    total = h_offsets[P];
-    int longest = 0;
-    for (int i = 0; i < P; ++i) longest = std::max(longest, h_offsets[i + 1] - h_offsets[i]);
-    f->max_prog_ops = longest;
-    if (!auto_tic || longest <= kProgOpsTarget || TIC <= 4) break;
+    if (!auto_tic || f->max_list_units <= kPieceUnitsTarget || TIC <= 4) break;
     TIC /= 2;
   }
   f->tile_ic = TIC;
   f->n_oc_blocks = B; f->n_stages = T;
+  f->n_list_units = (int64_t)h_offsets[P] + 2;
+  if (cudaMalloc(&f->d_lists, (size_t)f->n_list_units * sizeof(uint64_t)) != cudaSuccess) {
+    cudaGetLastError();
+    set_error("cudaMalloc of %lld list units failed", (long long)f->n_list_units);
+    return fail(TETRIS_ERR_NOMEM);
+  }
+  if ((rc = list_fill(d_dense, in_channel, out_channel, kernel_size, K, TIC, B, T,
+                      f->d_list_offsets, f->d_lists, f->n_list_units, 0)))
+    return fail(rc);
+  // ---- PROGRAM form (generic kernel, interpreter kernel) ----
+  if (!alloc_offsets(&f->d_prog_offsets)) {
+    cudaGetLastError();
+    set_error("cudaMalloc of compressor scratch failed");
+    return fail(TETRIS_ERR_NOMEM);
+  }
+  if ((rc = compress_count(d_dense, in_channel, out_channel, kernel_size, K, TIC, B, T, d_scratch, 0)) ||
+      (rc = compress_scan(d_scratch, f->d_prog_offsets, P, 0)))
+    return fail(rc);
+  unsigned long long nnz = 0;
+  if (!fetch_offsets(f->d_prog_offsets, &f->max_prog_ops) ||
+      cudaMemcpy(&nnz, compress_nnz_ptr(d_scratch, P), sizeof(nnz), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    set_error("compressor count/scan failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return fail(TETRIS_ERR_CUDA);
+  }
+  const int32_t total = h_offsets[P];
   f->nnz = (int64_t)nnz;
   f->n_ops = (int64_t)total + kTailPadOps;
   if (cudaMalloc(&f->d_ops, (size_t)f->n_ops * sizeof(uint64_t)) != cudaSuccess) {
@@ -217,6 +248,8 @@ void tetris_filter_destroy(tetris_filter_t *f) {
   DeviceGuard guard(f->device);
   cudaFree(f->d_ops);
   cudaFree(f->d_prog_offsets);
+  cudaFree(f->d_lists);
+  cudaFree(f->d_list_offsets);
   cudaFree(f->d_dense);
   delete f;
 }
@@ -228,12 +261,12 @@ int tetris_filter_info(const tetris_filter_t *f, tetris_filter_info_t *info) {
   info->kernel_size = f->kernel_size; info->groups = f->groups;
   info->oc_block = f->oc_block; info->tile_ic = f->tile_ic;
   info->n_oc_blocks = f->n_oc_blocks; info->n_stages = f->n_stages;
-  info->nnz = f->nnz; info->n_ops = f->n_ops;
+  info->nnz = f->nnz; info->n_ops = f->n_ops; info->n_list_units = f->n_list_units;
   info->compressed_bytes =
       f->groups != 1
           ? (int64_t)f->out_channel * f->kernel_size * f->kernel_size * (int64_t)sizeof(float)
-          : f->n_ops * (int64_t)sizeof(uint64_t) +
-                ((int64_t)f->n_oc_blocks * f->n_stages + 1) * (int64_t)sizeof(int32_t);
+          : (f->n_ops + f->n_list_units) * (int64_t)sizeof(uint64_t) +
+                2 * ((int64_t)f->n_oc_blocks * f->n_stages + 1) * (int64_t)sizeof(int32_t);
   info->device = f->device;
   return TETRIS_OK;
 }
@@ -251,6 +284,23 @@ int tetris_filter_download(const tetris_filter_t *f, uint64_t *ops, size_t ops_c
     const size_t n = (size_t)f->n_oc_blocks * f->n_stages + 1;
     if (offsets_capacity < n) { set_error("offsets buffer too small"); return TETRIS_ERR_INVALID; }
     TETRIS_CUDA_TRY(cudaMemcpy(prog_offsets, f->d_prog_offsets, n * sizeof(int32_t), cudaMemcpyDeviceToHost));
+  }
+  return TETRIS_OK;
+}
+
+int tetris_filter_download_lists(const tetris_filter_t *f, uint64_t *units, size_t units_capacity,
+                                 int32_t *list_offsets, size_t offsets_capacity) {
+  if (!f) { set_error("filter handle is NULL"); return TETRIS_ERR_INVALID; }
+  if (f->groups != 1) { set_error("a depthwise filter has no lists"); return TETRIS_ERR_UNSUPPORTED; }
+  DeviceGuard guard(f->device);
+  if (units) {
+    if (units_capacity < (size_t)f->n_list_units) { set_error("units buffer too small"); return TETRIS_ERR_INVALID; }
+    TETRIS_CUDA_TRY(cudaMemcpy(units, f->d_lists, (size_t)f->n_list_units * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+  }
+  if (list_offsets) {
+    const size_t n = (size_t)f->n_oc_blocks * f->n_stages + 1;
+    if (offsets_capacity < n) { set_error("offsets buffer too small"); return TETRIS_ERR_INVALID; }
+    TETRIS_CUDA_TRY(cudaMemcpy(list_offsets, f->d_list_offsets, n * sizeof(int32_t), cudaMemcpyDeviceToHost));
   }
   return TETRIS_OK;
 }

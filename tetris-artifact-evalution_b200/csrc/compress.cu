@@ -135,7 +135,98 @@ fill_kernel(const float *__restrict__ filt, int IC, int OC, int KS, int K, int T
   for (long long i = pos + lane; i < stop; i += 32) ops[i] = make_op(0u, c_end);
 }
 
+// ---- LIST form ------------------------------------------------------------------------------
+// One warp per piece.  The weights of one output channel and one stage are TIC*KS*KS contiguous
+// floats, scanned 32 at a time; a ballot gives each nonzero its rank in the list.
+__device__ __forceinline__ int list_row_len(int IC, int KS, int TIC, int t) {
+  const int ics = min(TIC, IC - t * TIC);
+  return ics * KS * KS;
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+list_count_kernel(const float *__restrict__ filt, int IC, int OC, int KS, int K, int TIC, int B,
+                  int T, int32_t *__restrict__ lens) {
+  const int p = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (p >= B * T) return;
+  const int b = p / T, t = p - b * T;
+  const int row_len = list_row_len(IC, KS, TIC, t);
+  int total = 0;
+  for (int k = 0; k < K; ++k) {
+    const int oc = b * K + k;
+    if (oc >= OC) break;
+    const float *row = filt + ((size_t)oc * IC + (size_t)t * TIC) * KS * KS;
+    for (int e0 = 0; e0 < row_len; e0 += 32) {
+      const int e = e0 + lane;
+      const bool nz = e < row_len && row[e] != 0.f;
+      total += __popc(__ballot_sync(0xffffffffu, nz));
+    }
+  }
+  int len = list_header_units(K) + total + 1;  // header, records, sentinel
+  len = (len + kProgAlignOps - 1) / kProgAlignOps * kProgAlignOps;
+  if (lane == 0) lens[p] = len;
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+list_fill_kernel(const float *__restrict__ filt, int IC, int OC, int KS, int K, int TIC, int B,
+                 int T, const int32_t *__restrict__ offsets, uint64_t *__restrict__ units,
+                 long long n_units) {
+  const int p = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int P = B * T;
+  if (p >= P) return;
+  const int b = p / T, t = p - b * T;
+  const int row_len = list_row_len(IC, KS, TIC, t);
+  const int KK = KS * KS;
+  uint32_t *hdr = reinterpret_cast<uint32_t *>(units + offsets[p]);
+  long long pos = (long long)offsets[p] + list_header_units(K);
+  int total = 0;
+  for (int k = 0; k < K; ++k) {
+    const int oc = b * K + k;
+    int n_k = 0;
+    if (oc < OC) {
+      const float *row = filt + ((size_t)oc * IC + (size_t)t * TIC) * KK;
+      for (int e0 = 0; e0 < row_len; e0 += 32) {
+        const int e = e0 + lane;
+        const float v = e < row_len ? row[e] : 0.f;
+        const unsigned m = __ballot_sync(0xffffffffu, v != 0.f);
+        if (v != 0.f) {
+          const int icl = e / KK, rs = e - icl * KK, r = rs / KS, s = rs - r * KS;
+          units[pos + n_k + __popc(m & ((1u << lane) - 1u))] =
+              make_op(__float_as_uint(v), ((uint32_t)icl << 8) | ((uint32_t)r << 4) | (uint32_t)s);
+        }
+        n_k += __popc(m);
+      }
+    }
+    if (lane == 0) hdr[k] = (uint32_t)n_k;
+    pos += n_k;
+    total += n_k;
+  }
+  if (lane < kListHeaderWords) hdr[K + lane] = lane == 0 ? (uint32_t)total : 0u;
+  // sentinel, then zero padding up to the next piece (or through the tail after the last one)
+  const long long stop = (p + 1 < P) ? (long long)offsets[p + 1] : n_units;
+  for (long long i = pos + lane; i < stop; i += 32) units[i] = 0ull;
+}
+
 }  // namespace
+
+int list_count(const float *d_filter, int IC, int OC, int KS, int K, int TIC, int B, int T,
+               int32_t *d_lens, cudaStream_t st) {
+  const int P = B * T;
+  list_count_kernel<<<(P + kWarpsPerBlock - 1) / kWarpsPerBlock, kWarpsPerBlock * 32, 0, st>>>(
+      d_filter, IC, OC, KS, K, TIC, B, T, d_lens);
+  TETRIS_CUDA_TRY(cudaGetLastError());
+  return TETRIS_OK;
+}
+
+int list_fill(const float *d_filter, int IC, int OC, int KS, int K, int TIC, int B, int T,
+              const int32_t *d_offsets, uint64_t *d_units, int64_t n_units, cudaStream_t st) {
+  const int P = B * T;
+  list_fill_kernel<<<(P + kWarpsPerBlock - 1) / kWarpsPerBlock, kWarpsPerBlock * 32, 0, st>>>(
+      d_filter, IC, OC, KS, K, TIC, B, T, d_offsets, d_units, (long long)n_units);
+  TETRIS_CUDA_TRY(cudaGetLastError());
+  return TETRIS_OK;
+}
 
 size_t compress_scratch_bytes(int n_programs) {
   // program lengths, then one 64-bit nonzero counter (8-byte aligned)

@@ -1,65 +1,58 @@
 // Tiled sparse-filter convolution for sm_100a: the hot kernel.
 //
 // Role of the reference's SparseConv2dKernel + LoadImg2SharedMem
-// (Tetris/spconv2d_kernel.cu:13-160), designed differently:
+// (Tetris/spconv2d_kernel.cu:13-160), re-designed:
 //
-//  * lanes are output PIXELS, not output channels.  A lane owns P2 neighbouring output columns of
-//    one tile row in two "planes" (two images of the batch, or the upper and lower half of a
-//    tile when the batch is odd) and K output channels: K*P2 float2 accumulators in registers.
-//    Packing the two planes into one float2 lets every multiply-add be one packed FP32 FMA
-//    (fma.rn.f32x2), which halves the issue slots the arithmetic needs.
-//  * the weight stream of a warp is warp-uniform: all 32 lanes execute the same compressed
-//    PROGRAM (format.h).  A GROUP record loads the input window of one (input channel, filter
-//    row) from shared memory into registers once; every following FMA record -- any of the K
-//    channels, any filter column -- reuses it from registers.  The record's code selects, by a
-//    jump table, the straight-line block that updates accumulator row k with column shift s, so
-//    no register is ever indexed dynamically.  Shared memory traffic per multiply-add drops by
-//    the number of nonzero weights that share an input offset, which is what lifts the kernel
-//    above the one-shared-load-per-FMA ceiling of the reference design.
-//  * the input tile (with halo) is staged per input-channel stage with cp.async into a
-//    double-buffered shared tile whose layout makes the window loads conflict-free 16-byte
-//    loads: per channel, [chunk plane j][input row][segment] chunks of {col0.p0, col0.p1,
-//    col1.p0, col1.p1}, plus a small side region for the right-hand halo of each row.
-//    (TMA tiled loads do not fit: the source is channel-innermost NHWC while the tile needs the
-//    channel outermost and two planes interleaved, so the copy is an element-wise gather.)
+//  * lanes are output PIXELS, not output channels, and the weights are warp-uniform.  A lane owns
+//    P2 output columns of one tile row in two "planes" (two images of the batch, or the upper
+//    and lower half of a tile when the batch is odd) for the K output channels of its warp's
+//    block: K*P2 float2 accumulators.  The two planes share every weight, so each multiply-add
+//    is one packed FP32 FMA (fma.rn.f32x2): half the issue slots of scalar FMAs.
+//  * the weights of a block arrive as K lists of {weight, position} records (LIST form,
+//    format.h), staged into shared memory next to the input tile.  The k loop is unrolled, so
+//    accumulator row k is a compile-time register name; the record only carries a shared-memory
+//    offset.  There is no per-record decode in the inner loop (the reference decodes y/x/ic with
+//    shifts and masks per nonzero, Tetris/spconv2d_kernel.cu:103-105): positions are turned into
+//    byte offsets once per staged list, 32 records at a time, one per lane.
+//  * the input tile (with halo) is staged per input-channel stage by cp.async into a
+//    double-buffered tile of float2 {plane0, plane1} laid out [channel][column parity][row]
+//    [column]; lane `seg` of a row owns columns seg, seg+NSEG, seg+2*NSEG, ..., so for any
+//    filter column shift the 32 lanes read 32 consecutive float2 -- a conflict-free 8-byte load
+//    with no alignment constraint, which is what lets one code path serve every kernel size and
+//    stride.  (TMA tiled loads do not fit this tile: the NHWC source is channel-innermost while
+//    the tile is channel-outermost with two planes interleaved -- an element-wise gather.)
+//  * records and input windows are prefetched one record ahead across list boundaries, so the
+//    loop body is load-next / FMA-current with no dependent address arithmetic.
+//
+// The kernel moves one shared-memory word per multiply-add (the same ratio as the reference,
+// see the profile summaries for what that bounds); a variant that reuses a register-resident
+// window across the K channels through a jump-table interpreter is in conv_interp.cu.
 //
 // NHWC in, NHWC out, FP32, output fully overwritten -- the contract of the reference launcher
 // (Tetris/spconv2d_kernel.cu:163-188).
+#include <algorithm>
+
 #include "internal.h"
-#include "interp_gen.h"
 
 namespace tetris {
 namespace {
 
-constexpr int kWarps = 4;  // warps per CTA; each warp runs one output-channel block
-
-template <int KS, int S, int P2>
-struct WinCfg {
-  static constexpr int WIN = (P2 - 1) * S + KS;            // float2 window entries a lane reads
-  static constexpr int OWN = P2 * S / 2;                   // 16-byte chunks of its own columns
-  static constexpr int HALO = (KS > S) ? (KS - S + 1) / 2 : 0;  // chunks borrowed from the right
-  static constexpr int NCH = OWN + HALO;
-  static_assert(P2 % 2 == 0, "P2 must be even");
-  static_assert(2 * NCH >= WIN, "window must be covered by the chunks");
-  static_assert(HALO <= OWN, "halo chunks come from one neighbouring segment");
-};
-
 struct TiledParams {
   const float *in;
   float *out;
-  const uint2 *ops;
-  const int32_t *prog_offsets;
-  int N, H, W, IC, OC, OH, OW, P;
-  int TS, TH;            // segments per tile row, tile rows; TS*TH lanes are in use
+  const uint2 *lists;
+  const int32_t *list_offsets;
+  int N, H, W, IC, OC, OH, OW, P, KS, S;
+  int NSEG, TH;          // lanes per tile row, tile rows; NSEG*TH lanes are in use
   int tiles_w, tiles_h;  // tiles along OW and along OH
   int pair_mode;         // 0: planes are images 2j and 2j+1; 1: upper/lower TH rows of one image
-  int ROWS, CIN2;        // staged input rows / columns per plane
-  int cp16;              // bytes between chunk planes  (ROWS*TS*16)
-  int hbase;             // byte offset of the halo region inside a channel slab (OWN*cp16)
-  int icpitch;           // bytes per channel slab
-  int stage_bytes;       // TIC * icpitch
-  int n_entries;         // staging table entries: 2*ROWS*CIN2
-  int prog_bytes;        // shared bytes reserved per warp and buffer for its staged program
+  int ROWS, COLS;        // staged input rows / columns per plane
+  int RP;                // bytes per staged row
+  int PLP;               // bytes per column-parity plane (ROWS * RP)
+  int ICP;               // bytes per channel slab
+  int stage_bytes;       // TIC * ICP
+  int n_entries;         // staging table entries: ROWS * COLS
+  int list_bytes;        // shared bytes per warp and buffer for its staged list piece
   int T, B, TIC, tic_shift;
 };
 
@@ -75,16 +68,33 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+__device__ __forceinline__ float2 lds_f2(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint2 lds_u2(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u1(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts_u1(uint32_t a, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
 
-template <int KS, int S, int K, int P2, int MINB>
-__global__ void __launch_bounds__(kWarps * 32, MINB) conv_tiled_kernel(const TiledParams p) {
-  using C = WinCfg<KS, S, P2>;
+template <int K, int P2, int WARPS, int MINB>
+__global__ void __launch_bounds__(WARPS * 32, MINB) conv_tiled_kernel(const TiledParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(smem_raw);
-  // layout: [input tile 0][input tile 1][programs 0: kWarps x prog_bytes][programs 1]
-  //         [staging table: n_entries x {goff, soff}]
-  const uint32_t prog0 = smem0 + 2 * p.stage_bytes;
-  int2 *tab = reinterpret_cast<int2 *>(smem_raw + 2 * p.stage_bytes + 2 * kWarps * p.prog_bytes);
+  // layout: [input tile 0][input tile 1][lists 0: WARPS x list_bytes][lists 1]
+  //         [staging table: n_entries x {goff plane 0, goff plane 1, soff, -}]
+  const uint32_t lists0 = smem0 + 2 * p.stage_bytes;
+  int4 *tab = reinterpret_cast<int4 *>(smem_raw + 2 * p.stage_bytes + 2 * WARPS * p.list_bytes);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
@@ -101,66 +111,62 @@ __global__ void __launch_bounds__(kWarps * 32, MINB) conv_tiled_kernel(const Til
   } else {
     n0 = n1 = pr; h0 = th * 2 * p.TH; h1 = h0 + p.TH; v1 = h1 < p.OH;
   }
-  const int w0 = tw * p.TS * P2;
+  const int w0 = tw * p.NSEG * P2;
 
-  // ---- staging table: for every (plane, input row, input column) of the tile, where it comes
-  //      from in global memory and where it goes inside a channel slab ----
-  for (int e = tid; e < p.n_entries; e += kWarps * 32) {
-    const int ci = e % p.CIN2;
-    const int ri = (e / p.CIN2) % p.ROWS;
-    const int pl = e / (p.CIN2 * p.ROWS);
-    const int n = pl ? n1 : n0;
-    const int ih = (pl ? h1 : h0) * S + ri - p.P;
-    const int iw = w0 * S + ci - p.P;
-    const bool ok = (pl == 0 || v1) && ih >= 0 && ih < p.H && iw >= 0 && iw < p.W;
-    const int q = ci >> 1, slot = q / C::OWN, jj = q - slot * C::OWN;
-    const int chunk = slot < p.TS ? jj * p.cp16 + (ri * p.TS + slot) * 16
-                                  : p.hbase + (ri * C::HALO + jj) * 16;
-    tab[e] = make_int2(ok ? (int)((((long long)n * p.H + ih) * p.W + iw) * p.IC) : -1,
-                       chunk + (ci & 1) * 8 + pl * 4);
+  // ---- staging table: where every (input row, input column) of the tile comes from in global
+  //      memory, per plane, and where it goes inside a channel slab ----
+  for (int e = tid; e < p.n_entries; e += WARPS * 32) {
+    const int ci = e % p.COLS, ri = e / p.COLS;
+    const int iw = w0 * p.S + ci - p.P;
+    const int ih0 = h0 * p.S + ri - p.P, ih1 = h1 * p.S + ri - p.P;
+    const bool okw = iw >= 0 && iw < p.W;
+    const bool ok0 = okw && ih0 >= 0 && ih0 < p.H;
+    const bool ok1 = okw && v1 && ih1 >= 0 && ih1 < p.H;
+    tab[e] = make_int4(ok0 ? (int)((((long long)n0 * p.H + ih0) * p.W + iw) * p.IC) : -1,
+                       ok1 ? (int)((((long long)n1 * p.H + ih1) * p.W + iw) * p.IC) : -1,
+                       (ci % p.S) * p.PLP + ri * p.RP + (ci / p.S) * 8, 0);
   }
   __syncthreads();
 
-  const int b = blockIdx.y * kWarps + warp;  // output-channel block of this warp
+  const int b = blockIdx.y * WARPS + warp;  // output-channel block of this warp
   const bool warp_on = b < p.B;
 
-  const int icl_s = tid & (p.TIC - 1);  // this thread's channel inside a stage (staging role)
-  const int pe0 = tid >> p.tic_shift, pe_step = (kWarps * 32) >> p.tic_shift;
+  // staging role of this thread: plane (tid & 1), channel inside the stage, entry slot
+  const int pl_s = tid & 1;
+  const int icl_s = (tid >> 1) & (p.TIC - 1);
+  const int pe0 = tid >> (1 + p.tic_shift), pe_step = (WARPS * 32) >> (1 + p.tic_shift);
   auto issue_stage = [&](int t, int buf) {
-    const uint32_t dst_base = smem0 + buf * p.stage_bytes;
-    if (warp_on) {  // this warp's program of the stage, 16 bytes (two records) per copy
-      const int po = p.prog_offsets[b * p.T + t], pn = p.prog_offsets[b * p.T + t + 1];
-      const uint32_t dst_p = prog0 + (buf * kWarps + warp) * p.prog_bytes;
-      for (int i = lane; 2 * i < pn - po; i += 32) cp_async16(dst_p + i * 16, p.ops + po + 2 * i);
+    if (warp_on) {  // this warp's list piece of the stage, 16 bytes per copy
+      const int po = p.list_offsets[b * p.T + t], pn = p.list_offsets[b * p.T + t + 1];
+      const uint32_t dst_p = lists0 + (buf * WARPS + warp) * p.list_bytes;
+      for (int i = lane; 2 * i < pn - po; i += 32) cp_async16(dst_p + i * 16, p.lists + po + 2 * i);
     }
     const int ic = t * p.TIC + icl_s;
     if (ic < p.IC) {
       const float *src_c = p.in + ic;
-      const uint32_t dst_c = dst_base + icl_s * p.icpitch;
+      const uint32_t dst_c = smem0 + buf * p.stage_bytes + icl_s * p.ICP + pl_s * 4;
       for (int e = pe0; e < p.n_entries; e += pe_step) {
-        const int2 ent = tab[e];
-        cp_async4(dst_c + ent.y, src_c + (ent.x >= 0 ? ent.x : 0), ent.x >= 0 ? 4 : 0);
+        const int4 ent = tab[e];
+        const int g = pl_s ? ent.y : ent.x;
+        cp_async4(dst_c + ent.z, src_c + (g >= 0 ? g : 0), g >= 0 ? 4 : 0);
       }
     }
     cp_async_commit();
   };
 
-  // ---- this lane's pixels (compute role) ----
-  const bool lane_on = lane < p.TS * p.TH;
-  const int row = lane_on ? lane / p.TS : 0;
-  const int seg = lane_on ? lane % p.TS : 0;
-  const uint32_t rp = p.TS * 16;
-  const uint32_t own_base = ((row * S) * p.TS + seg) * 16;
-  uint32_t halo_base = 0, halo_rp = 0, halo_js = 0;
-  if constexpr (C::HALO > 0) {
-    const bool inner = seg + 1 < p.TS;
-    halo_base = inner ? own_base + 16 : p.hbase + (row * S) * C::HALO * 16;
-    halo_rp = inner ? rp : C::HALO * 16;
-    halo_js = inner ? (uint32_t)p.cp16 : 16u;
-  }
+  // ---- this lane's pixels (compute role): columns seg + q*NSEG of tile row `row` ----
+  const bool lane_on = lane < p.NSEG * p.TH;
+  const int row = lane_on ? lane / p.NSEG : 0;
+  const int seg = lane_on ? lane % p.NSEG : 0;
+  uint32_t xoff[P2];
+#pragma unroll
+  for (int q = 0; q < P2; ++q) xoff[q] = (row * p.S) * p.RP + (q * p.NSEG + seg) * 8;
 
-  using I = Interp<KS, S, K, P2>;
-  I::init();  // K*P2 packed accumulators, zeroed, in registers the interpreter names statically
+  float2 acc[K][P2];
+#pragma unroll
+  for (int k = 0; k < K; ++k)
+#pragma unroll
+    for (int q = 0; q < P2; ++q) acc[k][q] = make_float2(0.f, 0.f);
 
   issue_stage(0, 0);
 #pragma unroll 1
@@ -174,15 +180,50 @@ __global__ void __launch_bounds__(kWarps * 32, MINB) conv_tiled_kernel(const Til
     __syncthreads();
     if (warp_on) {
       const uint32_t sbase = smem0 + (t & 1) * p.stage_bytes;
-      I::run(prog0 + ((t & 1) * kWarps + warp) * p.prog_bytes, sbase + own_base, sbase + halo_base,
-             (uint32_t)p.icpitch, rp, halo_rp, (uint32_t)p.cp16, halo_js);
+      const uint32_t piece = lists0 + ((t & 1) * WARPS + warp) * p.list_bytes;
+      const uint32_t recs = piece + (K + kListHeaderWords) * 4;
+      // positions -> byte offsets inside the staged tile, one record per lane at a time
+      const int total = (int)lds_u1(piece + K * 4);
+      for (int i = lane; i < total; i += 32) {
+        const uint32_t pos = lds_u1(recs + i * 8 + 4);
+        const uint32_t icl = pos >> 8, r = (pos >> 4) & 15u, s = pos & 15u;
+        sts_u1(recs + i * 8 + 4, icl * p.ICP + r * p.RP + (s % p.S) * p.PLP + (s / p.S) * 8);
+      }
+      __syncwarp();
+      // list lengths, two 16-bit counts per register
+      uint32_t cnt[K / 2];
+#pragma unroll
+      for (int k = 0; k < K; k += 2)
+        cnt[k / 2] = lds_u1(piece + k * 4) | (lds_u1(piece + k * 4 + 4) << 16);
+
+      uint32_t rp = recs;
+      uint2 rec = lds_u2(rp);
+      float2 xn[P2];
+#pragma unroll
+      for (int q = 0; q < P2; ++q) xn[q] = lds_f2(sbase + xoff[q] + rec.y);
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int n = (k & 1) ? (int)(cnt[k / 2] >> 16) : (int)(cnt[k / 2] & 0xffffu);
+#pragma unroll 1
+        for (int j = 0; j < n; ++j) {
+          const float w = __uint_as_float(rec.x);
+          const float2 w2 = make_float2(w, w);
+          float2 x[P2];
+#pragma unroll
+          for (int q = 0; q < P2; ++q) x[q] = xn[q];
+          rp += 8;
+          rec = lds_u2(rp);  // the next record: next in this list, first of the next, or sentinel
+#pragma unroll
+          for (int q = 0; q < P2; ++q) xn[q] = lds_f2(sbase + xoff[q] + rec.y);
+#pragma unroll
+          for (int q = 0; q < P2; ++q) acc[k][q] = __ffma2_rn(w2, x[q], acc[k][q]);
+        }
+      }
     }
     __syncthreads();
   }
 
   // ---- epilogue: NHWC stores, K consecutive channels per pixel ----
-  float2 acc[K][P2];
-  I::read(acc);
   if (!warp_on || !lane_on) return;
   const int oc0 = b * K;
   const int kn = min(K, p.OC - oc0);
@@ -194,7 +235,7 @@ __global__ void __launch_bounds__(kWarps * 32, MINB) conv_tiled_kernel(const Til
     if ((pl == 1 && !v1) || oh >= p.OH) continue;
 #pragma unroll
     for (int q = 0; q < P2; ++q) {
-      const int ow = w0 + seg * P2 + q;
+      const int ow = w0 + q * p.NSEG + seg;
       if (ow >= p.OW) continue;
       float *o = p.out + (((size_t)n * p.OH + oh) * p.OW + ow) * p.OC + oc0;
       if (vec) {
@@ -218,42 +259,67 @@ __global__ void __launch_bounds__(kWarps * 32, MINB) conv_tiled_kernel(const Til
 
 // ---- host side: tile geometry -----------------------------------------------------------------
 struct Geometry {
-  int TS, TH, tiles_w, tiles_h, pair_mode, n_pairs;
-  int ROWS, CIN2, cp16, hbase, icpitch, n_entries;
+  int NSEG, TH, tiles_w, tiles_h, pair_mode, n_pairs;
+  int ROWS, COLS, RP, PLP, ICP, n_entries;
   size_t smem_bytes;
 };
 
-template <int KS, int S, int P2>
-bool choose_geometry(const ConvShape &s, int TIC, size_t smem_limit, size_t prog_total, Geometry *g) {
-  using C = WinCfg<KS, S, P2>;
+// Row pitch in 8-byte slots: at least `need`, chosen so that the 16 lanes of a half-warp (one
+// 128-byte shared-memory wavefront of 8-byte loads) fall into as many distinct slots mod 16 as
+// possible.
+int pick_row_slots(int need, int NSEG, int TH, int S) {
+  int best = need, best_conf = 1 << 30;
+  for (int rw = need; rw < need + 16; ++rw) {
+    int conf = 0;
+    for (int half = 0; half < 2; ++half) {
+      int seen[16] = {0};
+      for (int l = half * 16; l < half * 16 + 16; ++l) {
+        if (l >= NSEG * TH) continue;
+        const int row = l / NSEG, seg = l % NSEG;
+        const int slot = (row * S * rw + seg) & 15;
+        conf += seen[slot]++;
+      }
+    }
+    if (conf < best_conf) { best_conf = conf; best = rw; }
+  }
+  return best;
+}
+
+template <int P2>
+bool choose_geometry(const ConvShape &s, int TIC, size_t smem_limit, size_t list_total,
+                     int ctas_y, int sm_count, int max_resident, Geometry *g) {
   const int pair_mode = (s.N % 2 == 0) ? 0 : 1;
+  const int n_pairs = pair_mode ? s.N : s.N / 2;
   double best = 1e300;
   bool found = false;
-  for (int TS = 1; TS <= 32; ++TS) {
-    for (int TH = 1; TS * TH <= 32; ++TH) {
+  for (int NSEG = 1; NSEG <= 32; ++NSEG) {
+    for (int TH = 1; NSEG * TH <= 32; ++TH) {
       const int rows_per_tile = pair_mode ? 2 * TH : TH;
-      const int tiles_w = (s.OW + TS * P2 - 1) / (TS * P2);
+      const int tiles_w = (s.OW + NSEG * P2 - 1) / (NSEG * P2);
       const int tiles_h = (s.OH + rows_per_tile - 1) / rows_per_tile;
-      const int ROWS = (TH - 1) * S + KS;
-      const int CIN2 = 2 * (TS * C::OWN + C::HALO);
-      int icpitch = (C::OWN * ROWS * TS + ROWS * C::HALO) * 16;
-      if (((icpitch / 16) & 1) == 0) icpitch += 16;  // odd chunk pitch: fewer staging conflicts
-      const int n_entries = 2 * ROWS * CIN2;
-      const size_t smem = 2 * (size_t)TIC * icpitch + (size_t)n_entries * sizeof(int2) + prog_total;
+      const int ROWS = (TH - 1) * s.S + s.KS;
+      const int COLS = (NSEG * P2 - 1) * s.S + s.KS;
+      const int RW = pick_row_slots((COLS + s.S - 1) / s.S, NSEG, TH, s.S);
+      const int RP = RW * 8, PLP = ROWS * RP;
+      int ICP = s.S * PLP;
+      if (((ICP / 8) & 1) == 0) ICP += 8;  // odd slot pitch: conflict-free staging stores
+      const int n_entries = ROWS * COLS;
+      const size_t smem = 2 * (size_t)TIC * ICP + (size_t)n_entries * sizeof(int4) + list_total;
       if (smem > smem_limit) continue;
-      // cost model: every tile runs one full warp program per stage whatever its lane use;
-      // staging grows with the staged area.
-      const double cost = (double)tiles_w * tiles_h * (2300.0 + 1.2 * ROWS * CIN2);
+      // Cost model: a tile runs one warp program per stage whatever its lane use; staging grows
+      // with the staged area; the grid runs in waves of `slots` resident CTAs.
+      const double ctas = (double)tiles_w * tiles_h * n_pairs * ctas_y;
+      const size_t per_sm = std::min<size_t>((size_t)max_resident, smem_limit / smem);
+      const double slots = (double)sm_count * (double)std::max<size_t>(1, per_sm);
+      const double waves = (double)((long long)((ctas + slots - 1) / slots));
+      const double per_cta = 3000.0 + 2.0 * ROWS * COLS;
+      const double cost = waves * per_cta + 1e-3 * ctas * per_cta;
       if (cost < best) {
         best = cost;
         found = true;
-        g->TS = TS; g->TH = TH; g->tiles_w = tiles_w; g->tiles_h = tiles_h;
-        g->pair_mode = pair_mode;
-        g->n_pairs = pair_mode ? s.N : s.N / 2;
-        g->ROWS = ROWS; g->CIN2 = CIN2;
-        g->cp16 = ROWS * TS * 16;
-        g->hbase = C::OWN * ROWS * TS * 16;
-        g->icpitch = icpitch;
+        g->NSEG = NSEG; g->TH = TH; g->tiles_w = tiles_w; g->tiles_h = tiles_h;
+        g->pair_mode = pair_mode; g->n_pairs = n_pairs;
+        g->ROWS = ROWS; g->COLS = COLS; g->RP = RP; g->PLP = PLP; g->ICP = ICP;
         g->n_entries = n_entries;
         g->smem_bytes = smem;
       }
@@ -262,44 +328,54 @@ bool choose_geometry(const ConvShape &s, int TIC, size_t smem_limit, size_t prog
   return found;
 }
 
-template <int KS, int S, int K, int P2, int MINB>
+template <int K, int P2, int WARPS, int MINB>
 int launch_instance(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                     cudaStream_t st) {
   Geometry g;
-  const size_t smem_limit = 200 * 1024 / MINB;
-  // one record of slack: the interpreter prefetches one record past END
-  const int prog_bytes = ((f->max_prog_ops + 2) * 8 + 15) / 16 * 16;
-  if (!choose_geometry<KS, S, P2>(s, f->tile_ic, smem_limit, (size_t)2 * kWarps * prog_bytes, &g)) {
-    set_error("tiled kernel: no tile geometry fits shared memory");
+  // MINB resident CTAs per SM is the register target; a tile that needs more shared memory than
+  // that leaves room for still runs, at lower occupancy.
+  const size_t smem_limit = (size_t)225 * 1024;
+  const int list_bytes = (f->max_list_units * 8 + 15) / 16 * 16;
+  const int ctas_y = (f->n_oc_blocks + WARPS - 1) / WARPS;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    TETRIS_CUDA_TRY(cudaGetDevice(&dev));
+    TETRIS_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  if (!choose_geometry<P2>(s, f->tile_ic, smem_limit, (size_t)2 * WARPS * list_bytes, ctas_y,
+                           sm_count, MINB, &g)) {
+    set_error("tiled kernel: no tile geometry fits shared memory (tile_ic=%d, list piece %d bytes)",
+              f->tile_ic, list_bytes);
     return TETRIS_ERR_UNSUPPORTED;
   }
   TiledParams p;
   p.in = in; p.out = out;
-  p.ops = reinterpret_cast<const uint2 *>(f->d_ops);
-  p.prog_offsets = f->d_prog_offsets;
+  p.lists = reinterpret_cast<const uint2 *>(f->d_lists);
+  p.list_offsets = f->d_list_offsets;
   p.N = s.N; p.H = s.H; p.W = s.W; p.IC = s.IC; p.OC = s.OC; p.OH = s.OH; p.OW = s.OW; p.P = s.P;
-  p.TS = g.TS; p.TH = g.TH; p.tiles_w = g.tiles_w; p.tiles_h = g.tiles_h;
+  p.KS = s.KS; p.S = s.S;
+  p.NSEG = g.NSEG; p.TH = g.TH; p.tiles_w = g.tiles_w; p.tiles_h = g.tiles_h;
   p.pair_mode = g.pair_mode;
-  p.ROWS = g.ROWS; p.CIN2 = g.CIN2; p.cp16 = g.cp16; p.hbase = g.hbase; p.icpitch = g.icpitch;
-  p.stage_bytes = f->tile_ic * g.icpitch;
+  p.ROWS = g.ROWS; p.COLS = g.COLS; p.RP = g.RP; p.PLP = g.PLP; p.ICP = g.ICP;
+  p.stage_bytes = f->tile_ic * g.ICP;
   p.n_entries = g.n_entries;
-  p.prog_bytes = prog_bytes;
+  p.list_bytes = list_bytes;
   p.T = f->n_stages; p.B = f->n_oc_blocks; p.TIC = f->tile_ic;
   p.tic_shift = 0;
   while ((1 << p.tic_shift) < f->tile_ic) ++p.tic_shift;
 
-  auto kern = conv_tiled_kernel<KS, S, K, P2, MINB>;
-  static thread_local size_t configured[16] = {0};  // per device: largest smem size opted into
+  auto kern = conv_tiled_kernel<K, P2, WARPS, MINB>;
+  static thread_local bool configured[16] = {false};  // per device: large shared memory opted in
   int dev = 0;
   TETRIS_CUDA_TRY(cudaGetDevice(&dev));
-  if (g.smem_bytes > 48 * 1024 && (dev >= 16 || configured[dev] < g.smem_bytes)) {
+  if (g.smem_bytes > 48 * 1024 && (dev >= 16 || !configured[dev])) {
     TETRIS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)(200 * 1024 / MINB)));
-    if (dev < 16) configured[dev] = 200 * 1024 / MINB;
+                                         (int)smem_limit));
+    if (dev < 16) configured[dev] = true;
   }
-  dim3 grid((unsigned)(g.tiles_w * g.tiles_h * g.n_pairs),
-            (unsigned)((f->n_oc_blocks + kWarps - 1) / kWarps));
-  kern<<<grid, kWarps * 32, g.smem_bytes, st>>>(p);
+  dim3 grid((unsigned)(g.tiles_w * g.tiles_h * g.n_pairs), (unsigned)ctas_y);
+  kern<<<grid, WARPS * 32, g.smem_bytes, st>>>(p);
   TETRIS_CUDA_TRY(cudaGetLastError());
   return TETRIS_OK;
 }
@@ -307,8 +383,8 @@ int launch_instance(const tetris_filter *f, const float *in, float *out, const C
 }  // namespace
 
 bool conv_tiled_supported(const tetris_filter *f, const ConvShape &s) {
-  if (f->groups != 1) return false;
-  if (!(s.KS == 1 || s.KS == 3) || !(s.S == 1 || s.S == 2)) return false;
+  if (f->groups != 1 || !f->d_lists) return false;
+  if (s.KS < 1 || s.KS > 8 || s.S < 1 || s.S > 4) return false;
   if (!(f->oc_block == 16 || f->oc_block == 8)) return false;
   const int tic = f->tile_ic;
   if (tic < 4 || tic > 32 || (tic & (tic - 1)) != 0) return false;
@@ -324,21 +400,8 @@ int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const
               f->oc_block, f->tile_ic);
     return TETRIS_ERR_UNSUPPORTED;
   }
-  const int K = f->oc_block;
-#define T_LAUNCH(KS_, S_, K_, MINB_)                                         \
-  if (s.KS == KS_ && s.S == S_ && K == K_)                                   \
-    return launch_instance<KS_, S_, K_, 4, MINB_>(f, in, out, s, st);
-  T_LAUNCH(3, 1, 16, 3)
-  T_LAUNCH(3, 2, 16, 3)
-  T_LAUNCH(1, 1, 16, 3)
-  T_LAUNCH(1, 2, 16, 3)
-  T_LAUNCH(3, 1, 8, 4)
-  T_LAUNCH(3, 2, 8, 4)
-  T_LAUNCH(1, 1, 8, 4)
-  T_LAUNCH(1, 2, 8, 4)
-#undef T_LAUNCH
-  set_error("tiled kernel: no instance");
-  return TETRIS_ERR_UNSUPPORTED;
+  if (f->oc_block == 16) return launch_instance<16, 4, 4, 3>(f, in, out, s, st);
+  return launch_instance<8, 4, 4, 4>(f, in, out, s, st);
 }
 
 }  // namespace tetris

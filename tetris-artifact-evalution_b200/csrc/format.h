@@ -23,7 +23,25 @@
 #pragma once
 #include <stdint.h>
 
+//
+// ---- the LIST form (consumed by the tiled kernel) ------------------------------------------
+// Same cut into (b, t) pieces, different order inside a piece: one list per output channel of
+// the block, each list in (ic, r, s) order -- again the reference's accumulation order.  Piece
+// layout, in 32-bit words:
+//
+//   [0 .. K)      n_k   records in the list of channel k
+//   [K]           total = sum of n_k
+//   [K+1 .. K+4)  zero
+//   then `total` 8-byte records {weight:f32, pos:u32}, lists back to back, k = 0 first,
+//   pos = (ic_local << 8) | (r << 4) | s;
+//   then one sentinel record {0, 0}, so a reader may always fetch "the next record".
+//
+// Pieces start on 16-byte boundaries; offsets are counted in 8-byte units.  Nothing depends on
+// the image size: the kernel turns `pos` into a shared-memory byte offset once per staged piece.
 namespace tetris {
+
+constexpr int kListHeaderWords = 4;  // words after the K counts: total + 3 zero words
+__host__ __device__ inline int list_header_units(int K) { return (K + kListHeaderWords) / 2; }
 
 constexpr int kProgAlignOps = 2;  // programs start at even record indices (16 bytes)
 constexpr int kTailPadOps = 16;   // END records after the last program

@@ -18,6 +18,11 @@ struct tetris_filter {
   uint64_t *d_ops;         // program stream (n_ops records incl. tail padding)
   int32_t *d_prog_offsets; // n_oc_blocks * n_stages + 1 record indices
   float *d_dense;          // depthwise only: dense [C][KS*KS] filter
+  // LIST form (format.h), consumed by the tiled kernel
+  uint64_t *d_lists;       // n_list_units 8-byte units incl. tail padding
+  int32_t *d_list_offsets; // n_oc_blocks * n_stages + 1 unit indices
+  int64_t n_list_units;
+  int max_list_units;      // longest piece, in 8-byte units
 };
 
 namespace tetris {
@@ -49,12 +54,20 @@ const unsigned long long *compress_nnz_ptr(const int32_t *d_scratch, int n_progr
 int compress_fill(const float *d_filter, int IC, int OC, int KS, int K, int TIC, int B, int T,
                   const int32_t *d_offsets, uint64_t *d_ops, int64_t n_ops, cudaStream_t st);
 
+int list_count(const float *d_filter, int IC, int OC, int KS, int K, int TIC, int B, int T,
+               int32_t *d_lens, cudaStream_t st);
+int list_fill(const float *d_filter, int IC, int OC, int KS, int K, int TIC, int B, int T,
+              const int32_t *d_offsets, uint64_t *d_units, int64_t n_units, cudaStream_t st);
+
 // conv_generic.cu / conv_tiled.cu / depthwise.cu / layout.cu
 int launch_conv_generic(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                         cudaStream_t st);
 bool conv_tiled_supported(const tetris_filter *f, const ConvShape &s);
 int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                       cudaStream_t st);
+bool conv_interp_supported(const tetris_filter *f, const ConvShape &s);
+int launch_conv_interp(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
+                       cudaStream_t st);
 int launch_depthwise(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                      cudaStream_t st);
 int launch_nchw_to_nhwc(const float *src, float *dst, int N, int C, int H, int W, cudaStream_t st);
