@@ -71,7 +71,8 @@ LIST_TAIL_UNITS = 2
 def pack_lists(w, K=16, TIC=16):
     """Dense OIHW float32 -> (units uint64[], piece_offsets int32[B*T+1]) of the LIST form:
     per piece K counts + total + 3 zero words, then the K lists of {weight, pos} records in
-    (ic, r, s) order, then a zero sentinel; pieces padded to an even number of 8-byte units."""
+    (ic, r, s) order, each padded to an even length with {0, TIC << 8}, then two such records as
+    sentinels; pieces padded to an even number of 8-byte units."""
     w = np.ascontiguousarray(w, np.float32)
     OC, IC, KS, _ = w.shape
     B, T = -(-OC // K), -(-IC // TIC)
@@ -89,12 +90,15 @@ def pack_lists(w, K=16, TIC=16):
                     for icl, r, s in zip(*np.nonzero(blk != 0)):  # row-major = (ic, r, s) order
                         recs += [int(bits[oc, t * TIC + icl, r, s]), (int(icl) << 8) | (int(r) << 4) | int(s)]
                         n += 1
+                if n % 2:                       # lists are padded to an even length
+                    recs += [0, TIC << 8]
+                    n += 1
                 counts.append(n)
-            words += counts + [sum(counts), 0, 0, 0] + recs + [0, 0]
+            words += counts + [sum(counts), 0, 0, 0] + recs + [0, TIC << 8] * 2
             while ((len(words) - start) // 2) % PROG_ALIGN_OPS:
-                words += [0, 0]
+                words += [0, TIC << 8]
             offsets.append(len(words) // 2)
-    words += [0, 0] * LIST_TAIL_UNITS
+    words += [0, TIC << 8] * LIST_TAIL_UNITS
     return np.array(words, np.uint32).view(np.uint64), np.array(offsets, np.int32)
 
 
@@ -113,6 +117,9 @@ def unpack_lists(units, offsets, OC, IC, KS, K=16, TIC=16):
                 for _ in range(int(counts[k])):
                     val, pos = int(words[i]), int(words[i + 1])
                     i += 2
+                    if pos == TIC << 8:
+                        assert val == 0  # a padding record
+                        continue
                     w[b * K + k, t * TIC + (pos >> 8), (pos >> 4) & 15, pos & 15] = val
-            assert words[i] == 0 and words[i + 1] == 0  # the sentinel
+            assert words[i] == 0 and words[i + 1] == TIC << 8  # the sentinels
     return w.view(np.float32)

@@ -156,13 +156,15 @@ list_count_kernel(const float *__restrict__ filt, int IC, int OC, int KS, int K,
     const int oc = b * K + k;
     if (oc >= OC) break;
     const float *row = filt + ((size_t)oc * IC + (size_t)t * TIC) * KS * KS;
+    int n_k = 0;
     for (int e0 = 0; e0 < row_len; e0 += 32) {
       const int e = e0 + lane;
       const bool nz = e < row_len && row[e] != 0.f;
-      total += __popc(__ballot_sync(0xffffffffu, nz));
+      n_k += __popc(__ballot_sync(0xffffffffu, nz));
     }
+    total += (n_k + 1) & ~1;  // lists are padded to an even length
   }
-  int len = list_header_units(K) + total + 1;  // header, records, sentinel
+  int len = list_header_units(K) + total + 2;  // header, records, two sentinels
   len = (len + kProgAlignOps - 1) / kProgAlignOps * kProgAlignOps;
   if (lane == 0) lens[p] = len;
 }
@@ -198,14 +200,17 @@ list_fill_kernel(const float *__restrict__ filt, int IC, int OC, int KS, int K, 
         n_k += __popc(m);
       }
     }
+    const uint64_t pad = make_op(0u, (uint32_t)TIC << 8);
+    if ((n_k & 1) && lane == 0) units[pos + n_k] = pad;
+    n_k = (n_k + 1) & ~1;
     if (lane == 0) hdr[k] = (uint32_t)n_k;
     pos += n_k;
     total += n_k;
   }
   if (lane < kListHeaderWords) hdr[K + lane] = lane == 0 ? (uint32_t)total : 0u;
-  // sentinel, then zero padding up to the next piece (or through the tail after the last one)
+  // sentinels, then the same padding record up to the next piece (or through the tail)
   const long long stop = (p + 1 < P) ? (long long)offsets[p + 1] : n_units;
-  for (long long i = pos + lane; i < stop; i += 32) units[i] = 0ull;
+  for (long long i = pos + lane; i < stop; i += 32) units[i] = make_op(0u, (uint32_t)TIC << 8);
 }
 
 }  // namespace

@@ -50,7 +50,7 @@ struct TiledParams {
   int RP;                // bytes per staged row
   int PLP;               // bytes per column-parity plane (ROWS * RP)
   int ICP;               // bytes per channel slab
-  int stage_bytes;       // TIC * ICP
+  int stage_bytes;       // (TIC + 1) * ICP: the staged channels and one all-zero slab
   int n_entries;         // staging table entries: ROWS * COLS
   int list_bytes;        // shared bytes per warp and buffer for its staged list piece
   int T, B, TIC, tic_shift;
@@ -76,6 +76,11 @@ __device__ __forceinline__ float2 lds_f2(uint32_t a) {
 __device__ __forceinline__ uint2 lds_u2(uint32_t a) {
   uint2 v;
   asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint4 lds_u4(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
   return v;
 }
 __device__ __forceinline__ uint32_t lds_u1(uint32_t a) {
@@ -155,9 +160,12 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) conv_tiled_kernel(const Tile
   };
 
   // ---- this lane's pixels (compute role): columns seg + q*NSEG of tile row `row` ----
+  // Idle lanes mirror the last active lane: same address, so their loads are broadcasts that
+  // add no shared-memory wavefront.
   const bool lane_on = lane < p.NSEG * p.TH;
-  const int row = lane_on ? lane / p.NSEG : 0;
-  const int seg = lane_on ? lane % p.NSEG : 0;
+  const int lane_c = min(lane, p.NSEG * p.TH - 1);
+  const int row = lane_c / p.NSEG;
+  const int seg = lane_c % p.NSEG;
   uint32_t xoff[P2];
 #pragma unroll
   for (int q = 0; q < P2; ++q) xoff[q] = (row * p.S) * p.RP + (q * p.NSEG + seg) * 8;
@@ -167,6 +175,13 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) conv_tiled_kernel(const Tile
   for (int k = 0; k < K; ++k)
 #pragma unroll
     for (int q = 0; q < P2; ++q) acc[k][q] = make_float2(0.f, 0.f);
+
+  // Channel slab TIC of each buffer stays zero: padding records point there, so a padded
+  // multiply-add adds exactly 0 whatever the input holds.
+  for (int i = tid * 4; i < p.ICP; i += WARPS * 32 * 4) {
+    sts_u1(smem0 + p.TIC * p.ICP + i, 0u);
+    sts_u1(smem0 + p.stage_bytes + p.TIC * p.ICP + i, 0u);
+  }
 
   issue_stage(0, 0);
 #pragma unroll 1
@@ -183,40 +198,51 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) conv_tiled_kernel(const Tile
       const uint32_t piece = lists0 + ((t & 1) * WARPS + warp) * p.list_bytes;
       const uint32_t recs = piece + (K + kListHeaderWords) * 4;
       // positions -> byte offsets inside the staged tile, one record per lane at a time
-      const int total = (int)lds_u1(piece + K * 4);
+      // (the sentinel pair behind the last list is translated too)
+      const int total = (int)lds_u1(piece + K * 4) + 2;
       for (int i = lane; i < total; i += 32) {
         const uint32_t pos = lds_u1(recs + i * 8 + 4);
         const uint32_t icl = pos >> 8, r = (pos >> 4) & 15u, s = pos & 15u;
         sts_u1(recs + i * 8 + 4, icl * p.ICP + r * p.RP + (s % p.S) * p.PLP + (s / p.S) * 8);
       }
       __syncwarp();
-      // list lengths, two 16-bit counts per register
+      // list lengths (even by construction), two 16-bit counts per register
       uint32_t cnt[K / 2];
 #pragma unroll
       for (int k = 0; k < K; k += 2)
         cnt[k / 2] = lds_u1(piece + k * 4) | (lds_u1(piece + k * 4 + 4) << 16);
-
-      uint32_t rp = recs;
-      uint2 rec = lds_u2(rp);
-      float2 xn[P2];
+      uint32_t xb[P2];
 #pragma unroll
-      for (int q = 0; q < P2; ++q) xn[q] = lds_f2(sbase + xoff[q] + rec.y);
+      for (int q = 0; q < P2; ++q) xb[q] = sbase + xoff[q];
+
+      // Two records per iteration, their windows in two register sets that swap roles, so the
+      // prefetch needs no register copies: load pair i+1 while the FMAs of pair i issue.
+      uint32_t rp = recs;
+      uint4 rr = lds_u4(rp);  // records i (x, y) and i+1 (z, w)
+      float2 xa[P2], xc[P2];
+#pragma unroll
+      for (int q = 0; q < P2; ++q) xa[q] = lds_f2(xb[q] + rr.y);
+#pragma unroll
+      for (int q = 0; q < P2; ++q) xc[q] = lds_f2(xb[q] + rr.w);
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const int n = (k & 1) ? (int)(cnt[k / 2] >> 16) : (int)(cnt[k / 2] & 0xffffu);
 #pragma unroll 1
-        for (int j = 0; j < n; ++j) {
-          const float w = __uint_as_float(rec.x);
-          const float2 w2 = make_float2(w, w);
-          float2 x[P2];
+        for (int j = 0; j < n; j += 2) {
+          const float wa = __uint_as_float(rr.x), wc = __uint_as_float(rr.z);
+          rp += 16;
+          rr = lds_u4(rp);  // the next pair: of this list, of the next one, or the sentinels
+          const float2 wa2 = make_float2(wa, wa), wc2 = make_float2(wc, wc);
 #pragma unroll
-          for (int q = 0; q < P2; ++q) x[q] = xn[q];
-          rp += 8;
-          rec = lds_u2(rp);  // the next record: next in this list, first of the next, or sentinel
+          for (int q = 0; q < P2; ++q) {
+            acc[k][q] = __ffma2_rn(wa2, xa[q], acc[k][q]);
+            xa[q] = lds_f2(xb[q] + rr.y);
+          }
 #pragma unroll
-          for (int q = 0; q < P2; ++q) xn[q] = lds_f2(sbase + xoff[q] + rec.y);
-#pragma unroll
-          for (int q = 0; q < P2; ++q) acc[k][q] = __ffma2_rn(w2, x[q], acc[k][q]);
+          for (int q = 0; q < P2; ++q) {
+            acc[k][q] = __ffma2_rn(wc2, xc[q], acc[k][q]);
+            xc[q] = lds_f2(xb[q] + rr.w);
+          }
         }
       }
     }
@@ -304,7 +330,7 @@ bool choose_geometry(const ConvShape &s, int TIC, size_t smem_limit, size_t list
       int ICP = s.S * PLP;
       if (((ICP / 8) & 1) == 0) ICP += 8;  // odd slot pitch: conflict-free staging stores
       const int n_entries = ROWS * COLS;
-      const size_t smem = 2 * (size_t)TIC * ICP + (size_t)n_entries * sizeof(int4) + list_total;
+      const size_t smem = 2 * (size_t)(TIC + 1) * ICP + (size_t)n_entries * sizeof(int4) + list_total;
       if (smem > smem_limit) continue;
       // Cost model: a tile runs one warp program per stage whatever its lane use; staging grows
       // with the staged area; the grid runs in waves of `slots` resident CTAs.
@@ -358,7 +384,7 @@ int launch_instance(const tetris_filter *f, const float *in, float *out, const C
   p.NSEG = g.NSEG; p.TH = g.TH; p.tiles_w = g.tiles_w; p.tiles_h = g.tiles_h;
   p.pair_mode = g.pair_mode;
   p.ROWS = g.ROWS; p.COLS = g.COLS; p.RP = g.RP; p.PLP = g.PLP; p.ICP = g.ICP;
-  p.stage_bytes = f->tile_ic * g.ICP;
+  p.stage_bytes = (f->tile_ic + 1) * g.ICP;
   p.n_entries = g.n_entries;
   p.list_bytes = list_bytes;
   p.T = f->n_stages; p.B = f->n_oc_blocks; p.TIC = f->tile_ic;
@@ -401,7 +427,7 @@ int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const
     return TETRIS_ERR_UNSUPPORTED;
   }
   if (f->oc_block == 16) return launch_instance<16, 4, 4, 3>(f, in, out, s, st);
-  return launch_instance<8, 4, 4, 4>(f, in, out, s, st);
+  return launch_instance<8, 4, 8, 2>(f, in, out, s, st);
 }
 
 }  // namespace tetris

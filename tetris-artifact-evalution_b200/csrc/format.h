@@ -29,12 +29,14 @@
 // the block, each list in (ic, r, s) order -- again the reference's accumulation order.  Piece
 // layout, in 32-bit words:
 //
-//   [0 .. K)      n_k   records in the list of channel k
+//   [0 .. K)      n_k   records in the list of channel k, padding included (always even)
 //   [K]           total = sum of n_k
 //   [K+1 .. K+4)  zero
 //   then `total` 8-byte records {weight:f32, pos:u32}, lists back to back, k = 0 first,
-//   pos = (ic_local << 8) | (r << 4) | s;
-//   then one sentinel record {0, 0}, so a reader may always fetch "the next record".
+//   pos = (ic_local << 8) | (r << 4) | s; a list with an odd number of nonzeros is padded with
+//   one record {0.0f, TIC << 8}: weight zero, position in the all-zero channel slab the kernel
+//   keeps behind the TIC staged ones, so the padded multiply-add adds exactly 0;
+//   then two such padding records as sentinels, so a reader may always fetch "the next pair".
 //
 // Pieces start on 16-byte boundaries; offsets are counted in 8-byte units.  Nothing depends on
 // the image size: the kernel turns `pos` into a shared-memory byte offset once per staged piece.
