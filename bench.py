@@ -49,7 +49,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -82,12 +82,13 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def build_layers(tb, wl, workload, batch, torch, device):
+def build_layers(tb, wl, workload, batch, torch, device, oc_block=0, tile_ic=0):
     """Compress every layer's filter on the device and allocate its NHWC input and output."""
     layers = []
     for idx, L in enumerate(wl.WORKLOADS[workload]()):
         filt = wl.make_filter(workload, idx, L)
-        f = tb.SparseFilter(filt, L.IC, L.OC, L.KS, groups=L.groups, device=device)
+        f = tb.SparseFilter(filt, L.IC, L.OC, L.KS, TILE_IC=tile_ic, groups=L.groups, device=device,
+                            oc_block=oc_block)
         oh, ow = wl.out_extent(L.H, L.KS, L.stride, L.pad), wl.out_extent(L.W, L.KS, L.stride, L.pad)
         g = torch.Generator(device="cuda").manual_seed(1000 + idx)
         x = torch.rand(batch, L.H, L.W, L.IC, device="cuda", generator=g)
@@ -165,12 +166,14 @@ def run_reference_arm(args, wl):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="vgg19")
     ap.add_argument("--batch", type=int, default=16, help="images per GPU")
     ap.add_argument("--variant", type=int, default=0, help="0 auto, 1 generic, 2 tiled")
+    ap.add_argument("--oc-block", type=int, default=0, help="output channels per register block (0 = default)")
+    ap.add_argument("--tile-ic", type=int, default=0, help="input channels per stage (0 = default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -193,7 +196,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     assert args.warmup >= 3, "at least 3 warm-up steps"
 
-    layers = build_layers(tb, wl, args.workload, args.batch, torch, local)
+    layers = build_layers(tb, wl, args.workload, args.batch, torch, local, args.oc_block, args.tile_ic)
     stream = torch.cuda.current_stream()
 
     def launch_all(events=None):

@@ -57,7 +57,7 @@ typedef struct tetris_filter tetris_filter_t; /* opaque; owns device buffers */
 
 /* Compression options; zero in a field means "engine default". */
 typedef struct {
-  int oc_block;  /* output channels per program (register block), 8 or 16          */
+  int oc_block;  /* output channels per register block, 8 (default) or 16            */
   int tile_ic;   /* input channels per stage, multiple of 4, <= 64                 */
   int reserved[6];
 } tetris_filter_opts_t;

@@ -66,7 +66,7 @@ def test_all_zero_filter_and_bad_arguments(tb, torch_cuda):
     f = tb.SparseFilter(w, 10, 20, 3)
     assert f.nnz_ == 0
     ops, offs = f.download()
-    assert np.all((ops >> np.uint64(32)) == 16 * 3 + 1)  # nothing but END records
+    assert np.all((ops >> np.uint64(32)) == f.info().oc_block * 3 + 1)  # nothing but END records
     with pytest.raises(tb.TetrisError) as e:
         tb.SparseFilter(np.zeros((4, 4, 9, 9), np.float32), 4, 4, 9)
     assert e.value.status == 1

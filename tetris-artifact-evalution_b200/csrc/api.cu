@@ -102,7 +102,7 @@ int tetris_filter_create_ex(const float *filter_oihw, int in_channel, int out_ch
     set_error("groups=%d: only 1 or depthwise (groups == ic == oc) is supported", groups);
     return TETRIS_ERR_UNSUPPORTED;
   }
-  const int K = opts && opts->oc_block ? opts->oc_block : 16;
+  const int K = opts && opts->oc_block ? opts->oc_block : 8;
   const bool auto_tic = !(opts && opts->tile_ic);
   int TIC = auto_tic ? 16 : opts->tile_ic;
   if (!(K == 8 || K == 16) || TIC < 4 || TIC > kMaxTileIc || (TIC & 3)) {
