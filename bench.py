@@ -193,6 +193,7 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
     torch.cuda.set_device(local)
     if world > 1:
+        os.environ["NCCL_DEBUG"] = "WARN"  # NCCL's version banner would land on stdout beside the JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     assert args.warmup >= 3, "at least 3 warm-up steps"
 
