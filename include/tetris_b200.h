@@ -156,6 +156,28 @@ int tetris_batch_slice(int batch_size, int world, int rank, int *begin, int *cou
 /* SM count, SM clock (kHz) and FP32 FMA lanes per SM of `device`. */
 int tetris_device_info(int device, int *sm_count, int *sm_clock_khz, int *fp32_lanes_per_sm);
 
+/*
+ * No counterpart in the reference.  The piece offsets of the list form of a dense OIHW filter
+ * that is ALREADY on the current device, written to `d_list_offsets`
+ * (ceil(OC/oc_block) * ceil(IC/tile_ic) + 1 ints, device memory of the caller), asynchronous on
+ * `stream` -- with no allocation of any kind, for callers that must not allocate where they
+ * call: processes that gave all device memory to one pool at start-up and forbid cudaMalloc on
+ * the request path, or code running inside another component's stream-ordered pipeline.  The
+ * result equals the offsets tetris_filter_download_lists returns for the same filter and options
+ * (the size a caller needs to reserve for the compressed filter is its last element + 2 units).
+ *  - The per-piece counts live in a fixed 64 KiB array inside the library image (16384 pieces);
+ *    more pieces than that are refused with TETRIS_ERR_UNSUPPORTED and a message.  Every GPU that
+ *    loads the library holds that array until the process exits.
+ *  - The first call on a device looks up the array's device address (once per device, that
+ *    device being current); make that first call before any stream capture begins.
+ *  - All calls share the array, so two calls that can overlap on the GPU (different streams, or
+ *    different host threads) race on it; keep calls on one device in stream order.  Nothing has
+ *    to be cleared between calls: each call rewrites every count it later reads.
+ */
+int tetris_list_offsets_noalloc(const float *d_filter_oihw, int in_channel, int out_channel,
+                                int kernel_size, int oc_block, int tile_ic,
+                                int32_t *d_list_offsets, void *stream);
+
 /* Text of the last error raised on this thread ("" if none). */
 const char *tetris_last_error(void);
 

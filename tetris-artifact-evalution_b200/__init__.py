@@ -72,6 +72,7 @@ SIGNATURES = {
     "tetris_conv2d_host_sharded": (_I, [ctypes.POINTER(_VP), _I, _VP, _VP, _I, _I, _I, _I, _I]),
     "tetris_batch_slice": (_I, [_I, _I, _I, _c_int_p, _c_int_p]),
     "tetris_device_info": (_I, [_I, _c_int_p, _c_int_p, _c_int_p]),
+    "tetris_list_offsets_noalloc": (_I, [_VP, _I, _I, _I, _I, _I, _VP, _VP]),
     "tetris_last_error": (ctypes.c_char_p, []),
 }
 
@@ -275,3 +276,13 @@ def device_info(device=0):
     a, b, c = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
     _check(lib().tetris_device_info(device, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)))
     return a.value, b.value, c.value
+
+
+def list_offsets_noalloc(d_filter, in_channel, out_channel, kernel_size, oc_block, tile_ic,
+                         d_list_offsets, cuda_stream=None):
+    """Piece offsets of the list form for a dense filter already on the device, written into the
+    caller's device array `d_list_offsets`; the library allocates nothing (fixed scratch inside
+    the library, at most 16384 pieces).  Asynchronous on `cuda_stream`."""
+    _check(lib().tetris_list_offsets_noalloc(_ptr(d_filter), in_channel, out_channel, kernel_size,
+                                             oc_block, tile_ic, _ptr(d_list_offsets),
+                                             _stream_ptr(cuda_stream)))
