@@ -17,6 +17,7 @@
  *   tetris_conv2d_launch      SparseConv2d<...>() launcher,
  *                             Tetris/spconv2d_kernel.cu:163-188
  *   tetris_conv2d_time        TimingTetrisSparseConv2d, Tetris/spconv2d.cc:29-69
+ *   tetris_conv2d_tune        GetTetrisSparseConv2dTime's tile search, Tetris/spconv2d.cc:72-329
  *   tetris_conv2d_host        CudaSparseConv2d's data path (host NCHW in, host
  *                             NCHW out), Tetris/spconv2d.cc:332-367
  *   tetris_nchw_to_nhwc/
@@ -123,6 +124,18 @@ int tetris_conv2d_time(const tetris_filter_t *f, const float *d_input_nhwc,
                        float *d_output_nhwc, int batch_size, int img_h, int img_w, int stride,
                        int padding, void *stream, int variant, int warm, int repeat,
                        float *ms_mean);
+
+/*
+ * Tile auto-tuning, the counterpart of the reference's search over its tile table
+ * (GetTetrisSparseConv2dTime, Tetris/spconv2d.cc:72-329): times the `max_candidates` (0 = 12)
+ * tile shapes / kernel instances that the engine's cost model ranks best, a few launches each,
+ * remembers the fastest with the filter for this conv shape (later launches use it) and stores
+ * its mean time in *best_ms (may be NULL).  Blocking; overwrites the output; untimed set-up work
+ * in the reference's protocol.  The filter is not rebuilt: one compressed form serves every tile.
+ */
+int tetris_conv2d_tune(const tetris_filter_t *f, const float *d_input_nhwc, float *d_output_nhwc,
+                       int batch_size, int img_h, int img_w, int stride, int padding, void *stream,
+                       int max_candidates, float *best_ms);
 
 /*
  * Host NCHW in, host NCHW out, blocking.  Copies the input to the device,

@@ -184,3 +184,19 @@ def test_timing_harness_runs(tb, torch_cuda):
     y = torch_cuda.empty(1, 56, 56, 64, device="cuda")
     ms = tb.timing_sparse_conv2d(f, x, y, 1, 56, 56, 1, 1, warm=3, repeat=10)
     assert 0.0 < ms < 50.0
+
+
+def test_tile_tuning_keeps_results_and_reports_a_time(tb, torch_cuda, oracle):
+    rng = np.random.default_rng(31)
+    filt = rng.normal(0, 0.05, (48, 32, 3, 3)).astype(np.float32)
+    filt[rng.random(filt.shape) < 0.9] = 0
+    x = rng.random((4, 32, 28, 28), dtype=np.float32)
+    f = tb.SparseFilter(filt, 32, 48, 3)
+    xin = torch_cuda.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
+    out = torch_cuda.empty(4, 28, 28, 48, device="cuda")
+    ms = tb.tune_sparse_conv2d(f, xin, out, 4, 28, 28, 1, 1, max_candidates=6)
+    assert 0.0 < ms < 10.0
+    got = device_conv(tb, torch_cuda, f, x, 1, 1, 0)   # launches now use the tuned tile shape
+    check(oracle, got, oracle.host_conv2d(x, filt, 1, 1))
+    got = device_conv(tb, torch_cuda, f, x[:3], 1, 1, 0)  # another shape: falls back to the model
+    check(oracle, got, oracle.host_conv2d(x[:3], filt, 1, 1))

@@ -66,6 +66,7 @@ SIGNATURES = {
     "tetris_conv2d_launch": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
     "tetris_conv2d_launch_ex": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I]),
     "tetris_conv2d_time": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _I, _I, _c_float_p]),
+    "tetris_conv2d_tune": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _c_float_p]),
     "tetris_conv2d_host": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
     "tetris_nchw_to_nhwc": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
     "tetris_nhwc_to_nchw": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
@@ -222,6 +223,17 @@ def timing_sparse_conv2d(sparse_filter, input, output, batch_size, img_h, img_w,
     _check(lib().tetris_conv2d_time(sparse_filter.handle, _ptr(input), _ptr(output), batch_size,
                                     img_h, img_w, stride, padding, _stream_ptr(cuda_stream), variant,
                                     warm, repeat, ctypes.byref(ms)))
+    return ms.value
+
+
+def tune_sparse_conv2d(sparse_filter, input, output, batch_size, img_h, img_w, stride, padding,
+                       cuda_stream=None, max_candidates=0):
+    """Time the best-ranked tile shapes for this conv shape, keep the fastest with the filter
+    (the reference's GetTetrisSparseConv2dTime search); returns its mean milliseconds."""
+    ms = ctypes.c_float(0.0)
+    _check(lib().tetris_conv2d_tune(sparse_filter.handle, _ptr(input), _ptr(output), batch_size, img_h,
+                                    img_w, stride, padding, _stream_ptr(cuda_stream), max_candidates,
+                                    ctypes.byref(ms)))
     return ms.value
 
 

@@ -104,7 +104,10 @@ int tetris_filter_create_ex(const float *filter_oihw, int in_channel, int out_ch
   }
   const int K = opts && opts->oc_block ? opts->oc_block : 8;
   const bool auto_tic = !(opts && opts->tile_ic);
-  int TIC = auto_tic ? 16 : opts->tile_ic;
+  // engine default: up to about 144 filter taps per channel block and stage (16 channels for 3x3,
+  // 32 for 1x1), halved below while the longest list piece is too long for shared memory
+  int TIC = auto_tic ? (kernel_size == 1 ? 32 : kernel_size == 2 ? 32 : kernel_size <= 4 ? 16 : 8)
+                     : opts->tile_ic;
   if (!(K == 8 || K == 16) || TIC < 4 || TIC > kMaxTileIc || (TIC & 3)) {
     set_error("bad compression options: oc_block=%d tile_ic=%d", K, TIC);
     return TETRIS_ERR_INVALID;
@@ -124,6 +127,7 @@ int tetris_filter_create_ex(const float *filter_oihw, int in_channel, int out_ch
   f->in_channel = in_channel; f->out_channel = out_channel; f->kernel_size = kernel_size;
   f->groups = groups; f->device = device;
   f->oc_block = K; f->tile_ic = TIC;
+  f->plan_cache = tiled_plan_cache_new();
 
   const size_t per_oc = depthwise ? 1 : (size_t)in_channel;
   const size_t dense_bytes = (size_t)out_channel * per_oc * kernel_size * kernel_size * sizeof(float);
@@ -250,6 +254,7 @@ void tetris_filter_destroy(tetris_filter_t *f) {
   cudaFree(f->d_prog_offsets);
   cudaFree(f->d_lists);
   cudaFree(f->d_list_offsets);
+  tiled_plan_cache_delete(f->plan_cache);
   cudaFree(f->d_dense);
   delete f;
 }
@@ -357,6 +362,24 @@ int tetris_conv2d_time(const tetris_filter_t *f, const float *d_input_nhwc,
   cudaEventElapsedTime(&ms, e0, e1);
   *ms_mean = ms / (float)repeat;
   return done(TETRIS_OK);
+}
+
+int tetris_conv2d_tune(const tetris_filter_t *f, const float *d_input_nhwc, float *d_output_nhwc,
+                       int batch_size, int img_h, int img_w, int stride, int padding, void *stream,
+                       int max_candidates, float *best_ms) {
+  ConvShape s;
+  int rc = make_shape(f, batch_size, img_h, img_w, stride, padding, &s);
+  if (rc) return rc;
+  if (!d_input_nhwc || !d_output_nhwc || batch_size < 1) { set_error("tuning needs real buffers and a non-empty batch"); return TETRIS_ERR_INVALID; }
+  if (max_candidates < 1) max_candidates = 12;
+  if (f->groups != 1 || !conv_tiled_supported(f, s)) {  // nothing to choose between: report the time
+    float ms = 0.f;
+    rc = tetris_conv2d_time(f, d_input_nhwc, d_output_nhwc, batch_size, img_h, img_w, stride, padding,
+                            stream, TETRIS_VARIANT_AUTO, 2, 5, &ms);
+    if (!rc && best_ms) *best_ms = ms;
+    return rc;
+  }
+  return tune_conv_tiled(f, d_input_nhwc, d_output_nhwc, s, (cudaStream_t)stream, max_candidates, best_ms);
 }
 
 int tetris_nchw_to_nhwc(const float *d_src, float *d_dst, int N, int C, int H, int W, void *stream) {

@@ -31,6 +31,11 @@
 // NHWC in, NHWC out, FP32, output fully overwritten -- the contract of the reference launcher
 // (Tetris/spconv2d_kernel.cu:163-188).
 #include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <mutex>
+#include <new>
+#include <vector>
 
 #include "internal.h"
 
@@ -284,15 +289,18 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) conv_tiled_kernel(const Tile
 }
 
 // ---- host side: tile geometry -----------------------------------------------------------------
-struct Geometry {
-  int NSEG, TH, tiles_w, tiles_h, pair_mode, n_pairs;
-  int ROWS, COLS, RP, PLP, ICP, n_entries;
-  size_t smem_bytes;
+struct Plan {
+  bool valid = false;
+  ConvShape shape{};
+  int instance = 0;  // which kernel template instance
+  TiledParams p{};
+  dim3 grid;
+  size_t smem_bytes = 0;
 };
 
 // Row pitch in 8-byte slots: at least `need`, chosen so that the 16 lanes of a half-warp (one
 // 128-byte shared-memory wavefront of 8-byte loads) fall into as many distinct slots mod 16 as
-// possible.
+// possible.  Idle lanes mirror the last active one and add no slot.
 int pick_row_slots(int need, int NSEG, int TH, int S) {
   int best = need, best_conf = 1 << 30;
   for (int rw = need; rw < need + 16; ++rw) {
@@ -311,112 +319,236 @@ int pick_row_slots(int need, int NSEG, int TH, int S) {
   return best;
 }
 
-template <int P2>
-bool choose_geometry(const ConvShape &s, int TIC, size_t smem_limit, size_t list_total,
-                     int ctas_y, int sm_count, int max_resident, Geometry *g) {
+constexpr size_t kSmemLimit = (size_t)225 * 1024;
+
+struct Instance {
+  int K, P2, WARPS, MINB;
+};
+constexpr Instance kInstances[] = {{8, 4, 8, 2}, {8, 2, 8, 3}, {16, 4, 4, 3}, {16, 2, 4, 4}};
+
+// Estimated launch time (in SM clocks) of one instance with one tile shape, or a negative value
+// if it does not fit.  The kernel is bound by the shared-memory data pipe (one wavefront per
+// clock and SM), so the model counts wavefronts: P2 window loads of 2 wavefronts plus half
+// a record load per weight record and warp, the staging stores, a fixed cost per CTA and per
+// stage, and the rounding of the grid to whole waves of resident CTAs.
+double plan_cost(const tetris_filter *f, const ConvShape &s, const Instance &inst, int NSEG, int TH,
+                 int sm_count, size_t smem_limit, Plan *out) {
+  const int P2 = inst.P2, TIC = f->tile_ic;
   const int pair_mode = (s.N % 2 == 0) ? 0 : 1;
   const int n_pairs = pair_mode ? s.N : s.N / 2;
-  double best = 1e300;
-  bool found = false;
-  for (int NSEG = 1; NSEG <= 32; ++NSEG) {
-    for (int TH = 1; NSEG * TH <= 32; ++TH) {
-      const int rows_per_tile = pair_mode ? 2 * TH : TH;
-      const int tiles_w = (s.OW + NSEG * P2 - 1) / (NSEG * P2);
-      const int tiles_h = (s.OH + rows_per_tile - 1) / rows_per_tile;
-      const int ROWS = (TH - 1) * s.S + s.KS;
-      const int COLS = (NSEG * P2 - 1) * s.S + s.KS;
-      const int RW = pick_row_slots((COLS + s.S - 1) / s.S, NSEG, TH, s.S);
-      const int RP = RW * 8, PLP = ROWS * RP;
-      int ICP = s.S * PLP;
-      if (((ICP / 8) & 1) == 0) ICP += 8;  // odd slot pitch: conflict-free staging stores
-      const int n_entries = ROWS * COLS;
-      const size_t smem = 2 * (size_t)(TIC + 1) * ICP + (size_t)n_entries * sizeof(int4) + list_total;
-      if (smem > smem_limit) continue;
-      // Cost model: a tile runs one warp program per stage whatever its lane use; staging grows
-      // with the staged area; the grid runs in waves of `slots` resident CTAs.
-      const double ctas = (double)tiles_w * tiles_h * n_pairs * ctas_y;
-      const size_t per_sm = std::min<size_t>((size_t)max_resident, smem_limit / smem);
-      const double slots = (double)sm_count * (double)std::max<size_t>(1, per_sm);
-      const double waves = (double)((long long)((ctas + slots - 1) / slots));
-      const double per_cta = 3000.0 + 2.0 * ROWS * COLS;
-      const double cost = waves * per_cta + 1e-3 * ctas * per_cta;
-      if (cost < best) {
-        best = cost;
-        found = true;
-        g->NSEG = NSEG; g->TH = TH; g->tiles_w = tiles_w; g->tiles_h = tiles_h;
-        g->pair_mode = pair_mode; g->n_pairs = n_pairs;
-        g->ROWS = ROWS; g->COLS = COLS; g->RP = RP; g->PLP = PLP; g->ICP = ICP;
-        g->n_entries = n_entries;
-        g->smem_bytes = smem;
-      }
-    }
+  const int rows_per_tile = pair_mode ? 2 * TH : TH;
+  const int tiles_w = (s.OW + NSEG * P2 - 1) / (NSEG * P2);
+  const int tiles_h = (s.OH + rows_per_tile - 1) / rows_per_tile;
+  const int ROWS = (TH - 1) * s.S + s.KS;
+  const int COLS = (NSEG * P2 - 1) * s.S + s.KS;
+  const int RW = pick_row_slots((COLS + s.S - 1) / s.S, NSEG, TH, s.S);
+  const int RP = RW * 8, PLP = ROWS * RP;
+  int ICP = s.S * PLP;
+  if (((ICP / 8) & 1) == 0) ICP += 8;  // odd slot pitch: conflict-free staging stores
+  const int n_entries = ROWS * COLS;
+  const int list_bytes = (f->max_list_units * 8 + 15) / 16 * 16;
+  const size_t smem = 2 * (size_t)(TIC + 1) * ICP + (size_t)n_entries * sizeof(int4) +
+                      (size_t)2 * inst.WARPS * list_bytes;
+  if (smem > smem_limit) return -1.0;
+  const int ctas_y = (f->n_oc_blocks + inst.WARPS - 1) / inst.WARPS;
+  const double ctas = (double)tiles_w * tiles_h * n_pairs * ctas_y;
+  const int resident = (int)std::max<size_t>(1, std::min<size_t>((size_t)inst.MINB, smem_limit / smem));
+  const double waves = ctas / ((double)sm_count * resident);
+  const double rounding = std::ceil(waves) / waves;
+  const double recs_per_block = 1.04 * (double)f->nnz / f->n_oc_blocks + 2.0 * f->n_stages;
+  const double wl = 2.0;  // an 8-byte load takes two passes whatever the number of active lanes (measured)
+  const double warp_blocks = (double)tiles_w * tiles_h * n_pairs * f->n_oc_blocks;
+  const double wf_compute = warp_blocks * recs_per_block * (P2 * wl + 0.5);
+  const double wf_staging = ctas * (double)f->n_stages * std::min(TIC, s.IC) * n_entries * 2 * 0.04;
+  const double fixed = ctas * (2500.0 + 300.0 * f->n_stages) / resident;
+  // a warp issues at most about one record per 36 clocks however idle the pipe is
+  const double t_issue = warp_blocks * recs_per_block * 36.0 / ((double)resident * inst.WARPS);
+  const double t = rounding * (std::max(wf_compute + wf_staging, t_issue) + fixed) / sm_count;
+  if (out) {
+    out->valid = true;
+    out->shape = s;
+    TiledParams &p = out->p;
+    p.lists = reinterpret_cast<const uint2 *>(f->d_lists);
+    p.list_offsets = f->d_list_offsets;
+    p.N = s.N; p.H = s.H; p.W = s.W; p.IC = s.IC; p.OC = s.OC; p.OH = s.OH; p.OW = s.OW; p.P = s.P;
+    p.KS = s.KS; p.S = s.S;
+    p.NSEG = NSEG; p.TH = TH; p.tiles_w = tiles_w; p.tiles_h = tiles_h;
+    p.pair_mode = pair_mode;
+    p.ROWS = ROWS; p.COLS = COLS; p.RP = RP; p.PLP = PLP; p.ICP = ICP;
+    p.stage_bytes = (TIC + 1) * ICP;
+    p.n_entries = n_entries;
+    p.list_bytes = list_bytes;
+    p.T = f->n_stages; p.B = f->n_oc_blocks; p.TIC = TIC;
+    p.tic_shift = 0;
+    while ((1 << p.tic_shift) < TIC) ++p.tic_shift;
+    out->grid = dim3((unsigned)(tiles_w * tiles_h * n_pairs), (unsigned)ctas_y);
+    out->smem_bytes = smem;
   }
-  return found;
+  return t;
+}
+
+struct Candidate {
+  double cost;
+  int instance, NSEG, TH;
+};
+
+// All (instance, tile shape) pairs that fit, cheapest first by the model.
+int enumerate_plans(const tetris_filter *f, const ConvShape &s, int *sm_count_out,
+                    std::vector<Candidate> *cands) {
+  int dev = 0, sm_count = 0;
+  TETRIS_CUDA_TRY(cudaGetDevice(&dev));
+  TETRIS_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  for (int i = 0; i < (int)(sizeof(kInstances) / sizeof(kInstances[0])); ++i) {
+    if (kInstances[i].K != f->oc_block) continue;
+    for (int NSEG = 1; NSEG <= 32; ++NSEG)
+      for (int TH = 1; NSEG * TH <= 32; ++TH) {
+        const double t = plan_cost(f, s, kInstances[i], NSEG, TH, sm_count, kSmemLimit, nullptr);
+        if (t >= 0.0) cands->push_back({t, i, NSEG, TH});
+      }
+  }
+  if (cands->empty()) {
+    set_error("tiled kernel: no tile geometry fits shared memory (tile_ic=%d, list piece %d units)",
+              f->tile_ic, f->max_list_units);
+    return TETRIS_ERR_UNSUPPORTED;
+  }
+  std::sort(cands->begin(), cands->end(),
+            [](const Candidate &a, const Candidate &b) { return a.cost < b.cost; });
+  *sm_count_out = sm_count;
+  return TETRIS_OK;
+}
+
+void fill_plan(const tetris_filter *f, const ConvShape &s, const Candidate &c, int sm_count, Plan *plan) {
+  plan_cost(f, s, kInstances[c.instance], c.NSEG, c.TH, sm_count, kSmemLimit, plan);
+  plan->instance = c.instance;
+}
+
+int make_plan(const tetris_filter *f, const ConvShape &s, Plan *plan) {
+  std::vector<Candidate> cands;
+  int sm_count = 0;
+  const int rc = enumerate_plans(f, s, &sm_count, &cands);
+  if (rc) return rc;
+  fill_plan(f, s, cands[0], sm_count, plan);
+  return TETRIS_OK;
 }
 
 template <int K, int P2, int WARPS, int MINB>
-int launch_instance(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
-                    cudaStream_t st) {
-  Geometry g;
-  // MINB resident CTAs per SM is the register target; a tile that needs more shared memory than
-  // that leaves room for still runs, at lower occupancy.
-  const size_t smem_limit = (size_t)225 * 1024;
-  const int list_bytes = (f->max_list_units * 8 + 15) / 16 * 16;
-  const int ctas_y = (f->n_oc_blocks + WARPS - 1) / WARPS;
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    TETRIS_CUDA_TRY(cudaGetDevice(&dev));
-    TETRIS_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
-  }
-  if (!choose_geometry<P2>(s, f->tile_ic, smem_limit, (size_t)2 * WARPS * list_bytes, ctas_y,
-                           sm_count, MINB, &g)) {
-    set_error("tiled kernel: no tile geometry fits shared memory (tile_ic=%d, list piece %d bytes)",
-              f->tile_ic, list_bytes);
-    return TETRIS_ERR_UNSUPPORTED;
-  }
-  TiledParams p;
-  p.in = in; p.out = out;
-  p.lists = reinterpret_cast<const uint2 *>(f->d_lists);
-  p.list_offsets = f->d_list_offsets;
-  p.N = s.N; p.H = s.H; p.W = s.W; p.IC = s.IC; p.OC = s.OC; p.OH = s.OH; p.OW = s.OW; p.P = s.P;
-  p.KS = s.KS; p.S = s.S;
-  p.NSEG = g.NSEG; p.TH = g.TH; p.tiles_w = g.tiles_w; p.tiles_h = g.tiles_h;
-  p.pair_mode = g.pair_mode;
-  p.ROWS = g.ROWS; p.COLS = g.COLS; p.RP = g.RP; p.PLP = g.PLP; p.ICP = g.ICP;
-  p.stage_bytes = (f->tile_ic + 1) * g.ICP;
-  p.n_entries = g.n_entries;
-  p.list_bytes = list_bytes;
-  p.T = f->n_stages; p.B = f->n_oc_blocks; p.TIC = f->tile_ic;
-  p.tic_shift = 0;
-  while ((1 << p.tic_shift) < f->tile_ic) ++p.tic_shift;
-
+int launch_instance(const Plan &plan, const float *in, float *out, cudaStream_t st) {
   auto kern = conv_tiled_kernel<K, P2, WARPS, MINB>;
   static thread_local bool configured[16] = {false};  // per device: large shared memory opted in
   int dev = 0;
   TETRIS_CUDA_TRY(cudaGetDevice(&dev));
-  if (g.smem_bytes > 48 * 1024 && (dev >= 16 || !configured[dev])) {
+  if (plan.smem_bytes > 48 * 1024 && (dev >= 16 || !configured[dev])) {
     TETRIS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem_limit));
+                                         (int)kSmemLimit));
     if (dev < 16) configured[dev] = true;
   }
-  dim3 grid((unsigned)(g.tiles_w * g.tiles_h * g.n_pairs), (unsigned)ctas_y);
-  kern<<<grid, WARPS * 32, g.smem_bytes, st>>>(p);
+  TiledParams p = plan.p;
+  p.in = in;
+  p.out = out;
+  kern<<<plan.grid, WARPS * 32, plan.smem_bytes, st>>>(p);
   TETRIS_CUDA_TRY(cudaGetLastError());
   return TETRIS_OK;
 }
 
+struct PlanCache {
+  std::mutex mutex;
+  Plan last;                 // plan of the most recent shape (a layer keeps one shape)
+  std::vector<Plan> tuned;   // plans chosen by timing (tetris_conv2d_tune); they win over `last`
+};
+
+bool same_shape(const ConvShape &a, const ConvShape &b) {
+  return a.N == b.N && a.H == b.H && a.W == b.W && a.IC == b.IC && a.OC == b.OC && a.KS == b.KS &&
+         a.S == b.S && a.P == b.P;
+}
+
 }  // namespace
+
+void *tiled_plan_cache_new() { return new (std::nothrow) PlanCache(); }
+void tiled_plan_cache_delete(void *c) { delete static_cast<PlanCache *>(c); }
 
 bool conv_tiled_supported(const tetris_filter *f, const ConvShape &s) {
   if (f->groups != 1 || !f->d_lists) return false;
   if (s.KS < 1 || s.KS > 8 || s.S < 1 || s.S > 4) return false;
   if (!(f->oc_block == 16 || f->oc_block == 8)) return false;
   const int tic = f->tile_ic;
-  if (tic < 4 || tic > 32 || (tic & (tic - 1)) != 0) return false;
+  if (tic < 4 || tic > 64 || (tic & (tic - 1)) != 0) return false;
   if ((long long)s.N * s.H * s.W * s.IC >= (1ll << 31)) return false;
   if (s.N < 1 || s.OH < 1 || s.OW < 1) return false;
   return true;
+}
+
+int launch_plan(const Plan &plan, const float *in, float *out, cudaStream_t st) {
+  // Every instance is bound by shared-memory bandwidth; the narrower register blocks fit more
+  // resident warps, the P2 = 2 instances trade a little more record traffic for twice the CTAs
+  // on small images.
+  switch (plan.instance) {
+    case 0: return launch_instance<8, 4, 8, 2>(plan, in, out, st);
+    case 1: return launch_instance<8, 2, 8, 3>(plan, in, out, st);
+    case 2: return launch_instance<16, 4, 4, 3>(plan, in, out, st);
+    default: return launch_instance<16, 2, 4, 4>(plan, in, out, st);
+  }
+}
+
+// Times the `max_candidates` plans the model ranks best (a few launches each, events on `st`),
+// keeps the fastest with the filter and reports its time.  The counterpart of the reference's
+// exhaustive tile search (Tetris/spconv2d.cc:285-311), without rebuilding the filter per tile.
+int tune_conv_tiled(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
+                    cudaStream_t st, int max_candidates, float *best_ms) {
+  if (!conv_tiled_supported(f, s)) {
+    set_error("tiled kernel does not cover this filter/shape");
+    return TETRIS_ERR_UNSUPPORTED;
+  }
+  std::vector<Candidate> cands;
+  int sm_count = 0;
+  int rc = enumerate_plans(f, s, &sm_count, &cands);
+  if (rc) return rc;
+  if ((int)cands.size() > max_candidates) cands.resize(max_candidates);
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  TETRIS_CUDA_TRY(cudaEventCreate(&e0));
+  if (cudaEventCreate(&e1) != cudaSuccess) { cudaEventDestroy(e0); set_error("cudaEventCreate failed"); return TETRIS_ERR_CUDA; }
+  Plan best_plan;
+  float best = -1.f;
+  const int reps = 5;
+  const bool debug = getenv("TETRIS_DEBUG_PLAN") != nullptr;  // prints every timed candidate
+  for (const Candidate &c : cands) {
+    Plan plan;
+    fill_plan(f, s, c, sm_count, &plan);
+    rc = launch_plan(plan, in, out, st);  // warm-up (also opts in to large shared memory)
+    if (rc) break;
+    cudaEventRecord(e0, st);
+    for (int i = 0; i < reps && !rc; ++i) rc = launch_plan(plan, in, out, st);
+    cudaEventRecord(e1, st);
+    if (rc) break;
+    if (cudaEventSynchronize(e1) != cudaSuccess) {
+      set_error("tuning launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+      rc = TETRIS_ERR_CUDA;
+      break;
+    }
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    ms /= reps;
+    if (debug)
+      fprintf(stderr, "[tetris tune] K=%d P2=%d warps=%d NSEG=%d TH=%d grid=%ux%u smem=%zu model=%.0f clk -> %.4f ms\n",
+              kInstances[c.instance].K, kInstances[c.instance].P2, kInstances[c.instance].WARPS, c.NSEG,
+              c.TH, plan.grid.x, plan.grid.y, plan.smem_bytes, c.cost, ms);
+    if (best < 0.f || ms < best) { best = ms; best_plan = plan; }
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (rc) return rc;
+  PlanCache *cache = static_cast<PlanCache *>(f->plan_cache);
+  if (cache) {
+    std::lock_guard<std::mutex> lock(cache->mutex);
+    bool replaced = false;
+    for (Plan &t : cache->tuned)
+      if (same_shape(t.shape, s)) { t = best_plan; replaced = true; }
+    if (!replaced) {
+      if (cache->tuned.size() >= 8) cache->tuned.erase(cache->tuned.begin());
+      cache->tuned.push_back(best_plan);
+    }
+  }
+  if (best_ms) *best_ms = best;
+  return TETRIS_OK;
 }
 
 int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
@@ -426,10 +558,26 @@ int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const
               f->oc_block, f->tile_ic);
     return TETRIS_ERR_UNSUPPORTED;
   }
-  // Both instances are bound by shared-memory bandwidth; the narrower register block fits more
-  // resident warps (measured: 8 channels x 8 warps is ~12 % faster on the VGG-19 layers).
-  if (f->oc_block == 16) return launch_instance<16, 4, 4, 3>(f, in, out, s, st);
-  return launch_instance<8, 4, 8, 2>(f, in, out, s, st);
+  // The tile shape and the kernel instance depend on the filter and the conv shape only; they
+  // are worked out once and kept with the filter.
+  Plan plan;
+  PlanCache *cache = static_cast<PlanCache *>(f->plan_cache);
+  bool hit = false;
+  if (cache) {
+    std::lock_guard<std::mutex> lock(cache->mutex);
+    for (const Plan &t : cache->tuned)
+      if (same_shape(t.shape, s)) { plan = t; hit = true; break; }
+    if (!hit && cache->last.valid && same_shape(cache->last.shape, s)) { plan = cache->last; hit = true; }
+  }
+  if (!hit) {
+    const int rc = make_plan(f, s, &plan);
+    if (rc) return rc;
+    if (cache) {
+      std::lock_guard<std::mutex> lock(cache->mutex);
+      cache->last = plan;
+    }
+  }
+  return launch_plan(plan, in, out, st);
 }
 
 }  // namespace tetris

@@ -23,6 +23,7 @@ struct tetris_filter {
   int32_t *d_list_offsets; // n_oc_blocks * n_stages + 1 unit indices
   int64_t n_list_units;
   int max_list_units;      // longest piece, in 8-byte units
+  void *plan_cache;        // tiled kernel: launch plan of the last conv shape (conv_tiled.cu)
 };
 
 namespace tetris {
@@ -65,6 +66,10 @@ int launch_conv_generic(const tetris_filter *f, const float *in, float *out, con
 bool conv_tiled_supported(const tetris_filter *f, const ConvShape &s);
 int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                       cudaStream_t st);
+int tune_conv_tiled(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
+                    cudaStream_t st, int max_candidates, float *best_ms);
+void *tiled_plan_cache_new();
+void tiled_plan_cache_delete(void *cache);
 bool conv_interp_supported(const tetris_filter *f, const ConvShape &s);
 int launch_conv_interp(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                        cudaStream_t st);

@@ -63,6 +63,7 @@ def main(argv=None):
     ap.add_argument("--repeat", type=int, default=None)
     ap.add_argument("--tile-ic", type=int, default=0)
     ap.add_argument("--oc-block", type=int, default=0)
+    ap.add_argument("--no-tune", action="store_true")
     ap.add_argument("--check", action="store_true")
     args = ap.parse_args(argv)
     print("args : %d %s\n" % (len(sys.argv), " ".join(sys.argv)))
@@ -98,6 +99,8 @@ def main(argv=None):
     oh, ow = tb.out_extent(h, ks, stride, pad), tb.out_extent(w, ks, stride, pad)
     xin = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
     out = torch.empty(batch, oh, ow, oc, device="cuda")
+    if not args.no_tune and args.variant in (0, 2):  # the reference times its best tile config
+        tb.tune_sparse_conv2d(f, xin, out, batch, h, w, stride, pad, cuda_stream=torch.cuda.current_stream())
     ms = tb.timing_sparse_conv2d(f, xin, out, batch, h, w, stride, pad,
                                  cuda_stream=torch.cuda.current_stream(), variant=args.variant,
                                  warm=tb.WARM if args.warm is None else args.warm,
