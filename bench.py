@@ -174,6 +174,8 @@ def main():
     ap.add_argument("--variant", type=int, default=0, help="0 auto, 1 generic, 2 tiled")
     ap.add_argument("--oc-block", type=int, default=0, help="output channels per register block (0 = default)")
     ap.add_argument("--tile-ic", type=int, default=0, help="input channels per stage (0 = default)")
+    ap.add_argument("--cudnn-context", action="store_true",
+                    help="also time cuDNN's dense FP32 convolution on the same layers (context line)")
     ap.add_argument("--no-tune", action="store_true", help="skip the untimed tile auto-tuning pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -280,6 +282,37 @@ def main():
             dist.destroy_process_group()
         return
 
+    # ---- context line: cuDNN dense FP32 convolution (a library, not this engine) on the same
+    #      shapes, as the reference does with CuDNNConv2d (Tetris/cuda_utils.cc:6-132) ----
+    cudnn = None
+    if args.cudnn_context:
+        import torch.nn.functional as F
+        torch.backends.cudnn.benchmark = True          # cuDNN picks its fastest algorithm per shape
+        torch.backends.cudnn.allow_tf32 = False        # FP32 arithmetic, like the engine
+        torch.backends.cuda.matmul.allow_tf32 = False
+        dense = []
+        for l in layers:
+            L = l["L"]
+            w = torch.from_numpy(l["filt"]).cuda().contiguous(memory_format=torch.channels_last)
+            x = l["x"].permute(0, 3, 1, 2)             # NHWC storage seen as NCHW channels_last
+            dense.append((x, w, L))
+        def cudnn_step():
+            for x, w, L in dense:
+                F.conv2d(x, w, None, L.stride, L.pad, 1, L.groups)
+        for _ in range(3):
+            cudnn_step()
+        torch.cuda.synchronize()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(3, min(args.steps, 10))
+        c0.record()
+        for _ in range(reps):
+            cudnn_step()
+        c1.record()
+        torch.cuda.synchronize()
+        cms = c0.elapsed_time(c1) / reps
+        cudnn = {"ms_per_step": cms, "images_per_s": args.batch / (cms * 1e-3), "dtype": "f32 (TF32 off)",
+                 "layout": "channels_last", "note": "dense convolution by cuDNN through torch; context, not a target"}
+
     # ---- roofline of the dominant kernel ----
     hbm_gbs, peak_src = read_peaks()
     sms, khz, lanes = tb.device_info(local)
@@ -340,6 +373,7 @@ def main():
         "gpu_launches": args.steps * len(layers), "clocks": clocks,
         "model_roofline_frac": t_roof_sum / (sum(layer_ms) * 1e-3),
         "step_ms_min_max": [min(step_ms), max(step_ms)],
+        "cudnn_context": cudnn,
         "per_layer": per_layer,
     }))
     if world > 1:
