@@ -140,12 +140,16 @@ int tetris_conv2d_tune(const tetris_filter_t *f, const float *d_input_nhwc, floa
 /*
  * Host NCHW in, host NCHW out, blocking.  Copies the input to the device,
  * transposes it to NHWC there, runs the convolution, transposes back and
- * copies the result out.  Device buffers are allocated and freed inside.
+ * copies the result out.  The device buffers come from a per-device workspace that
+ * grows on demand and is kept between calls (tetris_release_workspace frees it).
  * `h_input` is not modified.
  */
 int tetris_conv2d_host(const tetris_filter_t *f, const float *h_input_nchw,
                        float *h_output_nchw, int batch_size, int img_h, int img_w, int stride,
                        int padding, void *stream);
+
+/* Frees the activation workspaces tetris_conv2d_host keeps on the devices it was used on. */
+void tetris_release_workspace(void);
 
 /* Device-side layout transposes (out of place), asynchronous on `stream`. */
 int tetris_nchw_to_nhwc(const float *d_src, float *d_dst, int N, int C, int H, int W,

@@ -68,6 +68,7 @@ SIGNATURES = {
     "tetris_conv2d_time": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _I, _I, _c_float_p]),
     "tetris_conv2d_tune": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _c_float_p]),
     "tetris_conv2d_host": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
+    "tetris_release_workspace": (None, []),
     "tetris_nchw_to_nhwc": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
     "tetris_nhwc_to_nchw": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
     "tetris_conv2d_host_sharded": (_I, [ctypes.POINTER(_VP), _I, _VP, _VP, _I, _I, _I, _I, _I]),
@@ -266,6 +267,11 @@ def cuda_sparse_conv2d_sharded(h_input, sparse_filters, batch_size, img_h, img_w
                                             h_output.ctypes.data, batch_size, img_h, img_w, stride,
                                             padding))
     return h_output
+
+
+def release_workspace():
+    """Free the device workspaces that cuda_sparse_conv2d keeps between calls."""
+    lib().tetris_release_workspace()
 
 
 def nchw_to_nhwc(src, dst, N, C, H, W, cuda_stream=None):

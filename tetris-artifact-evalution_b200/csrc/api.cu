@@ -4,6 +4,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <mutex>
 #include <new>
 #include <string>
 #include <thread>
@@ -23,6 +24,15 @@ void set_error(const char *fmt, ...) {
 }
 
 namespace {
+
+// Activation workspace of tetris_conv2d_host, one per device, grown on demand.
+struct Workspace {
+  std::mutex mutex;
+  void *ptr = nullptr;
+  size_t bytes = 0;
+};
+constexpr int kMaxWsDevices = 64;
+Workspace g_workspace[kMaxWsDevices];
 
 // Makes `device` current for the lifetime of the object and restores the previous one.
 struct DeviceGuard {
@@ -403,16 +413,35 @@ int tetris_conv2d_host(const tetris_filter_t *f, const float *h_input_nchw,
   if (!guard.ok) { set_error("cudaSetDevice(%d) failed", f->device); return TETRIS_ERR_CUDA; }
   cudaStream_t st = (cudaStream_t)stream;
   const size_t in_elems = (size_t)s.N * s.IC * s.H * s.W, out_elems = (size_t)s.N * s.OC * s.OH * s.OW;
-  // One allocation: [input NCHW | input NHWC | output NHWC | output NCHW]
+  // One buffer: [input NCHW | input NHWC | output NHWC | output NCHW].  It comes from a
+  // grow-only per-device workspace that is kept between calls (tetris_release_workspace frees
+  // it); a call that finds the workspace in use by another thread allocates its own.
+  const size_t need = (2 * in_elems + 2 * out_elems) * sizeof(float);
+  Workspace *ws = f->device < kMaxWsDevices ? &g_workspace[f->device] : nullptr;
+  const bool cached = ws && ws->mutex.try_lock();
   float *d = nullptr;
-  if (cudaMalloc(&d, (2 * in_elems + 2 * out_elems) * sizeof(float)) != cudaSuccess) {
+  if (cached) {
+    if (ws->bytes < need) {
+      cudaFree(ws->ptr);
+      ws->ptr = nullptr; ws->bytes = 0;
+      if (cudaMalloc(&ws->ptr, need) == cudaSuccess) ws->bytes = need;
+    }
+    d = static_cast<float *>(ws->ptr);
+  } else if (cudaMalloc(&d, need) != cudaSuccess) {
+    d = nullptr;
+  }
+  if (!d) {
     cudaGetLastError();
-    set_error("cudaMalloc of %zu bytes of activations failed", (2 * in_elems + 2 * out_elems) * sizeof(float));
+    if (cached) ws->mutex.unlock();
+    set_error("cudaMalloc of %zu bytes of activations failed", need);
     return TETRIS_ERR_NOMEM;
   }
   float *d_in_nchw = d, *d_in_nhwc = d + in_elems, *d_out_nhwc = d + 2 * in_elems,
         *d_out_nchw = d + 2 * in_elems + out_elems;
-  auto done = [&](int code) { cudaFree(d); return code; };
+  auto done = [&](int code) {
+    if (cached) ws->mutex.unlock(); else cudaFree(d);
+    return code;
+  };
   if (cudaMemcpyAsync(d_in_nchw, h_input_nchw, in_elems * sizeof(float), cudaMemcpyHostToDevice, st) != cudaSuccess) {
     set_error("host-to-device copy failed: %s", cudaGetErrorString(cudaGetLastError()));
     return done(TETRIS_ERR_CUDA);
@@ -426,6 +455,20 @@ int tetris_conv2d_host(const tetris_filter_t *f, const float *h_input_nchw,
     return done(TETRIS_ERR_CUDA);
   }
   return done(TETRIS_OK);
+}
+
+void tetris_release_workspace(void) {
+  int prev = -1;
+  cudaGetDevice(&prev);
+  for (int dev = 0; dev < kMaxWsDevices; ++dev) {
+    Workspace &ws = g_workspace[dev];
+    std::lock_guard<std::mutex> lock(ws.mutex);
+    if (!ws.ptr) continue;
+    if (cudaSetDevice(dev) == cudaSuccess) cudaFree(ws.ptr);
+    ws.ptr = nullptr;
+    ws.bytes = 0;
+  }
+  if (prev >= 0) cudaSetDevice(prev);
 }
 
 int tetris_batch_slice(int batch_size, int world, int rank, int *begin, int *count) {

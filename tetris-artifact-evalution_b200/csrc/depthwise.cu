@@ -2,18 +2,80 @@
 //
 // The reference has no grouped convolution: it reads `groups` from the layer file and ignores it
 // (Tetris/tensor_utils.cc:66, Tetris/spconv2d.cc:404-406).  The MobileNet workload keeps its
-// depthwise filters dense, so this is a plain bandwidth-bound stencil: lanes run along the
-// channel axis (innermost in NHWC), so every global access is coalesced, and taps are added in
-// (r, s) order -- the order the CPU loop nest uses (Tetris/tensor_utils.cc:152-153).
+// depthwise filters dense, so this is a plain bandwidth-bound stencil.  Lanes run along the
+// channel axis (innermost in NHWC) four channels at a time, so every global access is a
+// coalesced 16-byte access; a thread produces a short run of output columns and keeps the input
+// columns it has loaded in registers, so each input value is read once per filter row instead of
+// once per tap.  Taps are added in (r, s) order -- the order the CPU loop nest uses
+// (Tetris/tensor_utils.cc:152-153).
 #include "internal.h"
 
 namespace tetris {
 namespace {
 
-template <int KS>
+// 3x3, stride S, four channels per thread, TW output columns per thread.
+template <int S, int TW>
 __global__ void __launch_bounds__(256)
-depthwise_kernel(const float *__restrict__ in, float *__restrict__ out,
-                 const float *__restrict__ filt, ConvShape s) {
+depthwise3x3_kernel(const float4 *__restrict__ in, float4 *__restrict__ out,
+                    const float *__restrict__ filt, ConvShape s, int cq, int wtiles) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)s.N * s.OH * wtiles * cq;
+  if (idx >= total) return;
+  const int q = (int)(idx % cq);
+  long long rest = idx / cq;
+  const int wt = (int)(rest % wtiles);
+  rest /= wtiles;
+  const int oh = (int)(rest % s.OH);
+  const int n = (int)(rest / s.OH);
+  const int ow0 = wt * TW;
+
+  float4 w[9];
+#pragma unroll
+  for (int t = 0; t < 9; ++t) {
+    w[t].x = __ldg(&filt[(size_t)(4 * q + 0) * 9 + t]);
+    w[t].y = __ldg(&filt[(size_t)(4 * q + 1) * 9 + t]);
+    w[t].z = __ldg(&filt[(size_t)(4 * q + 2) * 9 + t]);
+    w[t].w = __ldg(&filt[(size_t)(4 * q + 3) * 9 + t]);
+  }
+  float4 acc[TW];
+#pragma unroll
+  for (int j = 0; j < TW; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  constexpr int NCOL = (TW - 1) * S + 3;  // input columns this thread touches per row
+  const int iw0 = ow0 * S - s.P;
+  const float4 *img = in + (size_t)n * s.H * s.W * cq + q;
+#pragma unroll
+  for (int r = 0; r < 3; ++r) {
+    const int ih = oh * S + r - s.P;
+    if (ih < 0 || ih >= s.H) continue;
+    float4 x[NCOL];
+#pragma unroll
+    for (int c = 0; c < NCOL; ++c) {
+      const int iw = iw0 + c;
+      x[c] = (iw >= 0 && iw < s.W) ? __ldg(&img[((size_t)ih * s.W + iw) * cq])
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < TW; ++j)
+#pragma unroll
+      for (int t = 0; t < 3; ++t) {
+        const float4 xv = x[j * S + t], wv = w[r * 3 + t];
+        acc[j].x = fmaf(wv.x, xv.x, acc[j].x);
+        acc[j].y = fmaf(wv.y, xv.y, acc[j].y);
+        acc[j].z = fmaf(wv.z, xv.z, acc[j].z);
+        acc[j].w = fmaf(wv.w, xv.w, acc[j].w);
+      }
+  }
+  float4 *o = out + (((size_t)n * s.OH + oh) * s.OW + ow0) * cq + q;
+#pragma unroll
+  for (int j = 0; j < TW; ++j)
+    if (ow0 + j < s.OW) o[(size_t)j * cq] = acc[j];
+}
+
+// Any kernel size / stride / channel count: one output element per thread.
+__global__ void __launch_bounds__(256)
+depthwise_any_kernel(const float *__restrict__ in, float *__restrict__ out,
+                     const float *__restrict__ filt, ConvShape s) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long total = (long long)s.N * s.OH * s.OW * s.OC;
   if (idx >= total) return;
@@ -23,19 +85,16 @@ depthwise_kernel(const float *__restrict__ in, float *__restrict__ out,
   pix /= s.OW;
   const int oh = (int)(pix % s.OH);
   const int n = (int)(pix / s.OH);
-  const int ks = KS > 0 ? KS : s.KS;
   const float *img = in + (size_t)n * s.H * s.W * s.IC + c;
-  const float *w = filt + (size_t)c * ks * ks;
+  const float *w = filt + (size_t)c * s.KS * s.KS;
   float acc = 0.f;
-#pragma unroll
-  for (int r = 0; r < ks; ++r) {
+  for (int r = 0; r < s.KS; ++r) {
     const int ih = oh * s.S + r - s.P;
     if (ih < 0 || ih >= s.H) continue;
-#pragma unroll
-    for (int q = 0; q < ks; ++q) {
+    for (int q = 0; q < s.KS; ++q) {
       const int iw = ow * s.S + q - s.P;
       if (iw < 0 || iw >= s.W) continue;
-      acc = fmaf(__ldg(&w[r * ks + q]), __ldg(&img[((size_t)ih * s.W + iw) * s.IC]), acc);
+      acc = fmaf(__ldg(&w[r * s.KS + q]), __ldg(&img[((size_t)ih * s.W + iw) * s.IC]), acc);
     }
   }
   out[idx] = acc;
@@ -45,13 +104,24 @@ depthwise_kernel(const float *__restrict__ in, float *__restrict__ out,
 
 int launch_depthwise(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                      cudaStream_t st) {
-  const long long total = (long long)s.N * s.OH * s.OW * s.OC;
-  if (total <= 0) return TETRIS_OK;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
-  if (s.KS == 3)
-    depthwise_kernel<3><<<blocks, 256, 0, st>>>(in, out, f->d_dense, s);
-  else
-    depthwise_kernel<0><<<blocks, 256, 0, st>>>(in, out, f->d_dense, s);
+  const long long elems = (long long)s.N * s.OH * s.OW * s.OC;
+  if (elems <= 0) return TETRIS_OK;
+  const bool vec = s.KS == 3 && (s.S == 1 || s.S == 2) && (s.OC & 3) == 0 &&
+                   (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  if (vec) {
+    constexpr int TW = 4;
+    const int cq = s.OC / 4, wtiles = (s.OW + TW - 1) / TW;
+    const long long threads = (long long)s.N * s.OH * wtiles * cq;
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+    const float4 *in4 = reinterpret_cast<const float4 *>(in);
+    float4 *out4 = reinterpret_cast<float4 *>(out);
+    if (s.S == 1)
+      depthwise3x3_kernel<1, TW><<<blocks, 256, 0, st>>>(in4, out4, f->d_dense, s, cq, wtiles);
+    else
+      depthwise3x3_kernel<2, TW><<<blocks, 256, 0, st>>>(in4, out4, f->d_dense, s, cq, wtiles);
+  } else {
+    depthwise_any_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, st>>>(in, out, f->d_dense, s);
+  }
   TETRIS_CUDA_TRY(cudaGetLastError());
   return TETRIS_OK;
 }
