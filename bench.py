@@ -257,11 +257,18 @@ def main():
         for h, l in zip(hin, layers):
             h.copy_(l["x"].permute(0, 3, 1, 2))
 
+        hin_np = [h.numpy() for h in hin]
+        hout_np = [h.numpy() for h in hout]
+
         def e2e_step():
-            for h_in, h_out, l in zip(hin, hout, layers):
+            # host buffers in, host buffers out; two pipeline slots, so the upload of one layer
+            # overlaps the download of the previous one; every result is on the host at the end
+            for i, (h_in, h_out, l) in enumerate(zip(hin_np, hout_np, layers)):
                 L = l["L"]
-                tb.cuda_sparse_conv2d(h_in.numpy(), l["f"], args.batch, L.H, L.W, L.stride, L.pad,
-                                      h_output=h_out.numpy(), cuda_stream=stream)
+                tb.host_sync(local, i % 2)
+                tb.cuda_sparse_conv2d_async(h_in, l["f"], args.batch, L.H, L.W, L.stride, L.pad,
+                                            h_out, slot=i % 2)
+            tb.host_sync(local, -1)
         e2e_steps = max(1, min(args.steps, 3))
         e2e_step()
         barrier()

@@ -20,6 +20,8 @@
  *   tetris_conv2d_tune        GetTetrisSparseConv2dTime's tile search, Tetris/spconv2d.cc:72-329
  *   tetris_conv2d_host        CudaSparseConv2d's data path (host NCHW in, host
  *                             NCHW out), Tetris/spconv2d.cc:332-367
+ *   tetris_conv2d_host_async/
+ *   tetris_host_sync          no counterpart: the same data path, pipelined over slots
  *   tetris_nchw_to_nhwc/
  *   tetris_nhwc_to_nchw       NCHW2NHWC / NHWC2NCHW, Tetris/tensor_utils.cc:85-111,
  *                             done on the device
@@ -148,7 +150,21 @@ int tetris_conv2d_host(const tetris_filter_t *f, const float *h_input_nchw,
                        float *h_output_nchw, int batch_size, int img_h, int img_w, int stride,
                        int padding, void *stream);
 
-/* Frees the activation workspaces tetris_conv2d_host keeps on the devices it was used on. */
+/*
+ * The same data path without the final wait: the copies, transposes and the convolution are
+ * queued on an internal stream selected by `slot` (0..3; each slot has its own stream and
+ * workspace on the filter's device) and the call returns.  tetris_host_sync(device, slot) waits
+ * for a slot (slot < 0: all of them); until then neither host buffer may be touched.  Calls that
+ * alternate between slots overlap the upload of one with the download of the other.  Host buffers
+ * should be page-locked for the copies to be asynchronous.  No counterpart in the reference,
+ * whose CudaSparseConv2d is blocking.
+ */
+int tetris_conv2d_host_async(const tetris_filter_t *f, const float *h_input_nchw,
+                             float *h_output_nchw, int batch_size, int img_h, int img_w, int stride,
+                             int padding, int slot);
+int tetris_host_sync(int device, int slot);
+
+/* Frees the activation workspaces tetris_conv2d_host / _async keep on the devices it was used on. */
 void tetris_release_workspace(void);
 
 /* Device-side layout transposes (out of place), asynchronous on `stream`. */

@@ -48,3 +48,22 @@ def test_sharded_host_call_equals_single_call(tb, torch_cuda, oracle):
 def test_device_info(tb, torch_cuda):
     sms, khz, lanes = tb.device_info(0)
     assert sms > 0 and khz > 100000 and lanes == 128
+
+
+def test_pipelined_host_path_equals_the_blocking_one(tb, torch_cuda, oracle):
+    rng = np.random.default_rng(33)
+    filt = rng.normal(0, 0.05, (40, 24, 3, 3)).astype(np.float32)
+    filt[rng.random(filt.shape) < 0.85] = 0
+    f = tb.SparseFilter(filt, 24, 40, 3)
+    xs = [np.ascontiguousarray(rng.random((3, 24, 16 + i, 16), dtype=np.float32)) for i in range(5)]
+    outs = [np.full((3, 40, 16 + i, 16), np.nan, np.float32) for i in range(5)]
+    for i, (x, y) in enumerate(zip(xs, outs)):           # more calls than slots: slots get reused
+        tb.host_sync(0, i % 2)
+        tb.cuda_sparse_conv2d_async(x, f, 3, 16 + i, 16, 1, 1, y, slot=i % 2)
+    tb.host_sync(0, -1)
+    for i, (x, y) in enumerate(zip(xs, outs)):
+        assert np.array_equal(y, tb.cuda_sparse_conv2d(x, f, 3, 16 + i, 16, 1, 1))
+        assert oracle.compare(y, oracle.host_conv2d(x, filt, 1, 1))[0] == 0
+    with pytest.raises(tb.TetrisError):
+        tb.cuda_sparse_conv2d_async(xs[0], f, 3, 16, 16, 1, 1, outs[0], slot=9)
+    tb.release_workspace()

@@ -68,6 +68,8 @@ SIGNATURES = {
     "tetris_conv2d_time": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _I, _I, _c_float_p]),
     "tetris_conv2d_tune": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _c_float_p]),
     "tetris_conv2d_host": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
+    "tetris_conv2d_host_async": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _I]),
+    "tetris_host_sync": (_I, [_I, _I]),
     "tetris_release_workspace": (None, []),
     "tetris_nchw_to_nhwc": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
     "tetris_nhwc_to_nchw": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
@@ -267,6 +269,24 @@ def cuda_sparse_conv2d_sharded(h_input, sparse_filters, batch_size, img_h, img_w
                                             h_output.ctypes.data, batch_size, img_h, img_w, stride,
                                             padding))
     return h_output
+
+
+def cuda_sparse_conv2d_async(h_input, sparse_filter, batch_size, img_h, img_w, stride, padding,
+                             h_output, slot=0):
+    """Queue host NCHW -> host NCHW on pipeline slot `slot` and return; `h_input` / `h_output`
+    (contiguous float32 numpy arrays, ideally page-locked) must stay untouched until
+    host_sync(device, slot)."""
+    if not (h_input.flags.c_contiguous and h_output.flags.c_contiguous
+            and h_input.dtype == np.float32 and h_output.dtype == np.float32):
+        raise ValueError("the asynchronous path needs contiguous float32 host arrays")
+    _check(lib().tetris_conv2d_host_async(sparse_filter.handle, h_input.ctypes.data,
+                                          h_output.ctypes.data, batch_size, img_h, img_w, stride,
+                                          padding, slot))
+
+
+def host_sync(device=0, slot=-1):
+    """Wait for one pipeline slot of cuda_sparse_conv2d_async (slot < 0: all slots)."""
+    _check(lib().tetris_host_sync(device, slot))
 
 
 def release_workspace():

@@ -457,6 +457,77 @@ int tetris_conv2d_host(const tetris_filter_t *f, const float *h_input_nchw,
   return done(TETRIS_OK);
 }
 
+// ---- pipelined host-pointer path: `slot` selects one of kSlots (stream, workspace) pairs per
+//      device, so the upload of one call overlaps the download of the previous one ----
+namespace {
+constexpr int kSlots = 4;
+struct HostSlot {
+  std::mutex mutex;
+  cudaStream_t stream = nullptr;
+  void *ptr = nullptr;
+  size_t bytes = 0;
+};
+HostSlot g_slots[kMaxWsDevices][kSlots];
+}  // namespace
+
+int tetris_conv2d_host_async(const tetris_filter_t *f, const float *h_input_nchw,
+                             float *h_output_nchw, int batch_size, int img_h, int img_w, int stride,
+                             int padding, int slot) {
+  ConvShape s;
+  int rc = make_shape(f, batch_size, img_h, img_w, stride, padding, &s);
+  if (rc) return rc;
+  if (slot < 0 || slot >= kSlots || f->device >= kMaxWsDevices) {
+    set_error("slot %d outside [0, %d)", slot, kSlots);
+    return TETRIS_ERR_INVALID;
+  }
+  if (batch_size == 0) return TETRIS_OK;
+  if (!h_input_nchw || !h_output_nchw) { set_error("input or output pointer is NULL"); return TETRIS_ERR_INVALID; }
+  DeviceGuard guard(f->device);
+  if (!guard.ok) { set_error("cudaSetDevice(%d) failed", f->device); return TETRIS_ERR_CUDA; }
+  HostSlot &hs = g_slots[f->device][slot];
+  std::lock_guard<std::mutex> lock(hs.mutex);
+  if (!hs.stream) TETRIS_CUDA_TRY(cudaStreamCreateWithFlags(&hs.stream, cudaStreamNonBlocking));
+  const size_t in_elems = (size_t)s.N * s.IC * s.H * s.W, out_elems = (size_t)s.N * s.OC * s.OH * s.OW;
+  const size_t need = (2 * in_elems + 2 * out_elems) * sizeof(float);
+  if (hs.bytes < need) {
+    // the slot's earlier work may still read the old buffer
+    TETRIS_CUDA_TRY(cudaStreamSynchronize(hs.stream));
+    cudaFree(hs.ptr);
+    hs.ptr = nullptr; hs.bytes = 0;
+    if (cudaMalloc(&hs.ptr, need) != cudaSuccess) {
+      cudaGetLastError();
+      set_error("cudaMalloc of %zu bytes of activations failed", need);
+      return TETRIS_ERR_NOMEM;
+    }
+    hs.bytes = need;
+  }
+  float *d = static_cast<float *>(hs.ptr);
+  float *d_in_nchw = d, *d_in_nhwc = d + in_elems, *d_out_nhwc = d + 2 * in_elems,
+        *d_out_nchw = d + 2 * in_elems + out_elems;
+  cudaStream_t st = hs.stream;
+  TETRIS_CUDA_TRY(cudaMemcpyAsync(d_in_nchw, h_input_nchw, in_elems * sizeof(float), cudaMemcpyHostToDevice, st));
+  if ((rc = launch_nchw_to_nhwc(d_in_nchw, d_in_nhwc, s.N, s.IC, s.H, s.W, st))) return rc;
+  if ((rc = dispatch(f, d_in_nhwc, d_out_nhwc, s, st, TETRIS_VARIANT_AUTO))) return rc;
+  if ((rc = launch_nhwc_to_nchw(d_out_nhwc, d_out_nchw, s.N, s.OC, s.OH, s.OW, st))) return rc;
+  TETRIS_CUDA_TRY(cudaMemcpyAsync(h_output_nchw, d_out_nchw, out_elems * sizeof(float), cudaMemcpyDeviceToHost, st));
+  return TETRIS_OK;
+}
+
+int tetris_host_sync(int device, int slot) {
+  if (device < 0 || device >= kMaxWsDevices || slot >= kSlots) { set_error("bad device/slot"); return TETRIS_ERR_INVALID; }
+  DeviceGuard guard(device);
+  for (int i = 0; i < kSlots; ++i) {
+    if (slot >= 0 && i != slot) continue;
+    HostSlot &hs = g_slots[device][i];
+    std::lock_guard<std::mutex> lock(hs.mutex);
+    if (hs.stream && cudaStreamSynchronize(hs.stream) != cudaSuccess) {
+      set_error("pipelined convolution failed: %s", cudaGetErrorString(cudaGetLastError()));
+      return TETRIS_ERR_CUDA;
+    }
+  }
+  return TETRIS_OK;
+}
+
 void tetris_release_workspace(void) {
   int prev = -1;
   cudaGetDevice(&prev);
@@ -468,6 +539,16 @@ void tetris_release_workspace(void) {
     ws.ptr = nullptr;
     ws.bytes = 0;
   }
+  for (int dev = 0; dev < kMaxWsDevices; ++dev)
+    for (int i = 0; i < kSlots; ++i) {
+      HostSlot &hs = g_slots[dev][i];
+      std::lock_guard<std::mutex> lock(hs.mutex);
+      if (!hs.stream && !hs.ptr) continue;
+      if (cudaSetDevice(dev) != cudaSuccess) continue;
+      if (hs.stream) { cudaStreamSynchronize(hs.stream); cudaStreamDestroy(hs.stream); }
+      cudaFree(hs.ptr);
+      hs.stream = nullptr; hs.ptr = nullptr; hs.bytes = 0;
+    }
   if (prev >= 0) cudaSetDevice(prev);
 }
 
