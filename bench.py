@@ -360,7 +360,7 @@ def main():
     })
 
     cpu_baseline = None
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:  # the CPU baseline is a single-GPU-run extra
         threads = os.cpu_count() or 1
         secs, kind = cpu_reference_step(wl, args.workload, threads)
         cpu_baseline = {"value": 1.0 / secs, "unit": "images/s", "cores": threads, "kind": kind,
