@@ -52,8 +52,10 @@ enum {
   TETRIS_VARIANT_AUTO = 0,    /* fastest kernel that covers the shape              */
   TETRIS_VARIANT_GENERIC = 1, /* one thread per output pixel, any KS/stride        */
   TETRIS_VARIANT_TILED = 2,   /* shared-memory tile, per-channel weight lists          */
-  TETRIS_VARIANT_INTERP = 3   /* shared-memory tile, jump-table interpreter that reuses a
+  TETRIS_VARIANT_INTERP = 3,  /* shared-memory tile, jump-table interpreter that reuses a
                                  register-resident input window across channels (1x1, 3x3) */
+  TETRIS_VARIANT_TENSOR = 4   /* dense contraction on the tensor cores (tcgen05, split TF32);
+                                 stride 1, in_channel % 4 == 0                            */
 };
 
 typedef struct tetris_filter tetris_filter_t; /* opaque; owns device buffers */
@@ -104,6 +106,13 @@ int tetris_filter_download(const tetris_filter_t *f, uint64_t *ops, size_t ops_c
 /* The same for the list form: n_list_units 8-byte units and the per-piece unit offsets. */
 int tetris_filter_download_lists(const tetris_filter_t *f, uint64_t *units, size_t units_capacity,
                                  int32_t *list_offsets, size_t offsets_capacity);
+
+/*
+ * Waits for the device and reports whether any tensor-core launch of this filter gave up on one
+ * of its bounded barrier waits since the last check (TETRIS_ERR_CUDA; the output of that launch
+ * is invalid).  The other kernels have no waits that can fail.
+ */
+int tetris_filter_check(const tetris_filter_t *f);
 
 /*
  * Convolution, device pointers, NHWC in and NHWC out as in the reference

@@ -13,7 +13,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
-VARIANTS = {"auto": 0, "generic": 1, "tiled": 2, "interp": 3}
+VARIANTS = {"auto": 0, "generic": 1, "tiled": 2, "interp": 3, "tensor": 4}
 
 
 def device_conv(tb, torch, f, x_nchw, stride, pad, variant=0, poison=True):
@@ -25,12 +25,18 @@ def device_conv(tb, torch, f, x_nchw, stride, pad, variant=0, poison=True):
                      dtype=torch.float32, device="cuda")
     tb.sparse_conv2d(f, xin, out, n, h, w, stride, pad, variant=variant)
     torch.cuda.synchronize()
+    f.check()  # a tensor-core launch that gave up on a barrier would be reported here
     return out.cpu().numpy().transpose(0, 3, 1, 2)
 
 
-def covers(variant, ks, stride):
-    """The interpreter kernel is instantiated for 1x1 and 3x3, stride 1 and 2 only."""
-    return variant != "interp" or (ks in (1, 3) and stride in (1, 2))
+def covers(variant, ks, stride, ic=4):
+    """The interpreter kernel is instantiated for 1x1 and 3x3, stride 1 and 2 only; the
+    tensor-core variant covers stride 1 with in_channel a multiple of 4."""
+    if variant == "interp":
+        return ks in (1, 3) and stride in (1, 2)
+    if variant == "tensor":
+        return stride == 1 and ic % 4 == 0
+    return True
 
 
 def check(oracle, got, want):
@@ -40,14 +46,14 @@ def check(oracle, got, want):
     return max_rel
 
 
-@pytest.mark.parametrize("variant", ["generic", "tiled", "interp"])
+@pytest.mark.parametrize("variant", ["generic", "tiled", "interp", "tensor"])
 @pytest.mark.parametrize("path", GOLDEN, ids=lambda p: os.path.basename(p)[:-4])
 def test_golden_vectors(tb, torch_cuda, oracle, path, variant):
     z = np.load(path)
     x, w, stride, pad, want = z["input"], z["filter"], int(z["stride"]), int(z["pad"]), z["output"]
     oc, ic, ks, _ = w.shape
-    if not covers(variant, ks, stride):
-        pytest.skip("the interpreter kernel covers 1x1 and 3x3 only")
+    if not covers(variant, ks, stride, ic):
+        pytest.skip("shape outside what this variant covers")
     f = tb.SparseFilter(w, ic, oc, ks)
     got = device_conv(tb, torch_cuda, f, x, stride, pad, VARIANTS[variant])
     check(oracle, got, want)
@@ -90,7 +96,7 @@ SEEDED = [
 ]
 
 
-@pytest.mark.parametrize("variant", ["generic", "tiled", "interp"])
+@pytest.mark.parametrize("variant", ["generic", "tiled", "interp", "tensor"])
 @pytest.mark.parametrize("case", SEEDED, ids=lambda c: "n%d_ic%d_%dx%d_oc%d_k%d_s%d_p%d" % c[:8])
 def test_seeded_cases_against_oracle(tb, torch_cuda, oracle, case, variant):
     n, ic, h, w, oc, ks, stride, pad, density, K, TIC = case
@@ -99,8 +105,8 @@ def test_seeded_cases_against_oracle(tb, torch_cuda, oracle, case, variant):
     filt[rng.random(filt.shape) >= density] = 0
     x = rng.random((n, ic, h, w), dtype=np.float32)
     x[rng.random(x.shape) < 0.5] = 0
-    if not covers(variant, ks, stride):
-        pytest.skip("the interpreter kernel covers 1x1 and 3x3 only")
+    if not covers(variant, ks, stride, ic):
+        pytest.skip("shape outside what this variant covers")
     f = tb.SparseFilter(filt, ic, oc, ks, TILE_IC=TIC, oc_block=K)
     got = device_conv(tb, torch_cuda, f, x, stride, pad, VARIANTS[variant])
     check(oracle, got, oracle.host_conv2d(x, filt, stride, pad))
@@ -118,7 +124,7 @@ def test_skewed_rows_and_empty_channels(tb, torch_cuda, oracle):
     x = rng.standard_normal((2, ic, 20, 20)).astype(np.float32)
     f = tb.SparseFilter(filt, ic, oc, 3)
     want = oracle.host_conv2d(x, filt, 1, 1)
-    for v in (1, 2, 3):
+    for v in (1, 2, 3, 4):
         got = device_conv(tb, torch_cuda, f, x, 1, 1, v)
         check(oracle, got, want)
         assert np.all(got[:, [5, 40, 95]] == 0)
@@ -170,6 +176,8 @@ def test_full_size_properties_vgg_layer(tb, torch_cuda, workloads):
     yg = run(a, 1)
     assert torch.allclose(ya, yg, rtol=1e-4, atol=1e-5)
     assert torch.allclose(ya, run(a, 3), rtol=1e-4, atol=1e-5)
+    assert torch.allclose(ya, run(a, 4), rtol=1e-4, atol=1e-5)
+    f.check()
     lin = run(2.0 * a + b, 2)
     assert torch.allclose(lin, 2.0 * ya + run(b, 2), rtol=1e-4, atol=1e-4)
     one = run(a[3:4].contiguous(), 2, batch=1)   # odd batch takes the other pairing mode

@@ -31,7 +31,7 @@ LIB_PATH = os.path.join(_HERE, "libtetris_b200.so")
 WARM = 30     # Tetris/tensor_utils.h:11
 REPEAT = 100  # Tetris/tensor_utils.h:10
 
-VARIANT_AUTO, VARIANT_GENERIC, VARIANT_TILED, VARIANT_INTERP = 0, 1, 2, 3
+VARIANT_AUTO, VARIANT_GENERIC, VARIANT_TILED, VARIANT_INTERP, VARIANT_TENSOR = 0, 1, 2, 3, 4
 
 _c_float_p = ctypes.POINTER(ctypes.c_float)
 _c_int_p = ctypes.POINTER(ctypes.c_int)
@@ -63,6 +63,7 @@ SIGNATURES = {
     "tetris_filter_info": (_I, [_VP, ctypes.POINTER(FilterInfo)]),
     "tetris_filter_download": (_I, [_VP, _VP, ctypes.c_size_t, _VP, ctypes.c_size_t]),
     "tetris_filter_download_lists": (_I, [_VP, _VP, ctypes.c_size_t, _VP, ctypes.c_size_t]),
+    "tetris_filter_check": (_I, [_VP]),
     "tetris_conv2d_launch": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
     "tetris_conv2d_launch_ex": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I]),
     "tetris_conv2d_time": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _I, _I, _c_float_p]),
@@ -192,6 +193,10 @@ class SparseFilter:
         _check(lib().tetris_filter_download_lists(self._handle, units.ctypes.data, units.size,
                                                   offs.ctypes.data, offs.size))
         return units, offs
+
+    def check(self):
+        """Synchronise and raise if a tensor-core launch of this filter timed out on a barrier."""
+        _check(lib().tetris_filter_check(self._handle))
 
     @property
     def handle(self):

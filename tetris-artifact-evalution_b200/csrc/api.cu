@@ -75,6 +75,7 @@ int dispatch(const tetris_filter *f, const float *in, float *out, const ConvShap
     case TETRIS_VARIANT_GENERIC: return launch_conv_generic(f, in, out, s, st);
     case TETRIS_VARIANT_TILED: return launch_conv_tiled(f, in, out, s, st);
     case TETRIS_VARIANT_INTERP: return launch_conv_interp(f, in, out, s, st);
+    case TETRIS_VARIANT_TENSOR: return launch_conv_tc(f, in, out, s, st);
     case TETRIS_VARIANT_AUTO:
       return conv_tiled_supported(f, s) ? launch_conv_tiled(f, in, out, s, st)
                                         : launch_conv_generic(f, in, out, s, st);
@@ -247,6 +248,7 @@ int tetris_filter_create_ex(const float *filter_oihw, int in_channel, int out_ch
   if ((rc = compress_fill(d_dense, in_channel, out_channel, kernel_size, K, TIC, B, T,
                           f->d_prog_offsets, f->d_ops, f->n_ops, 0)))
     return fail(rc);
+  if ((rc = conv_tc_prepare(f, d_dense))) return fail(rc);
   if (cudaDeviceSynchronize() != cudaSuccess) {
     set_error("compressor fill failed: %s", cudaGetErrorString(cudaGetLastError()));
     return fail(TETRIS_ERR_CUDA);
@@ -265,6 +267,7 @@ void tetris_filter_destroy(tetris_filter_t *f) {
   cudaFree(f->d_lists);
   cudaFree(f->d_list_offsets);
   tiled_plan_cache_delete(f->plan_cache);
+  conv_tc_state_delete(f->tc_state);
   cudaFree(f->d_dense);
   delete f;
 }
@@ -316,6 +319,20 @@ int tetris_filter_download_lists(const tetris_filter_t *f, uint64_t *units, size
     const size_t n = (size_t)f->n_oc_blocks * f->n_stages + 1;
     if (offsets_capacity < n) { set_error("offsets buffer too small"); return TETRIS_ERR_INVALID; }
     TETRIS_CUDA_TRY(cudaMemcpy(list_offsets, f->d_list_offsets, n * sizeof(int32_t), cudaMemcpyDeviceToHost));
+  }
+  return TETRIS_OK;
+}
+
+int tetris_filter_check(const tetris_filter_t *f) {
+  if (!f) { set_error("filter handle is NULL"); return TETRIS_ERR_INVALID; }
+  DeviceGuard guard(f->device);
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    set_error("device error: %s", cudaGetErrorString(cudaGetLastError()));
+    return TETRIS_ERR_CUDA;
+  }
+  if (conv_tc_check_error(f)) {
+    set_error("a tensor-core launch of this filter gave up on a bounded barrier wait; its output is invalid");
+    return TETRIS_ERR_CUDA;
   }
   return TETRIS_OK;
 }

@@ -24,6 +24,7 @@ struct tetris_filter {
   int64_t n_list_units;
   int max_list_units;      // longest piece, in 8-byte units
   void *plan_cache;        // tiled kernel: launch plan of the last conv shape (conv_tiled.cu)
+  void *tc_state;          // tensor-core variant: split dense weights + tensor maps (conv_tc.cu)
 };
 
 namespace tetris {
@@ -73,6 +74,12 @@ void tiled_plan_cache_delete(void *cache);
 bool conv_interp_supported(const tetris_filter *f, const ConvShape &s);
 int launch_conv_interp(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                        cudaStream_t st);
+int conv_tc_prepare(tetris_filter *f, const float *d_dense);
+void conv_tc_state_delete(void *state);
+bool conv_tc_supported(const tetris_filter *f, const ConvShape &s);
+int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
+                   cudaStream_t st);
+int conv_tc_check_error(const tetris_filter *f);
 int launch_depthwise(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                      cudaStream_t st);
 int launch_nchw_to_nhwc(const float *src, float *dst, int N, int C, int H, int W, cudaStream_t st);
