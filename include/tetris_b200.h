@@ -49,7 +49,8 @@ enum {
 
 /* Kernel variants accepted by tetris_conv2d_launch_ex. */
 enum {
-  TETRIS_VARIANT_AUTO = 0,    /* fastest kernel that covers the shape              */
+  TETRIS_VARIANT_AUTO = 0,    /* fastest kernel that covers the shape: the tuned choice if
+                                 tetris_conv2d_tune ran for it, else the cost models'      */
   TETRIS_VARIANT_GENERIC = 1, /* one thread per output pixel, any KS/stride        */
   TETRIS_VARIANT_TILED = 2,   /* shared-memory tile, per-channel weight lists          */
   TETRIS_VARIANT_INTERP = 3,  /* shared-memory tile, jump-table interpreter that reuses a

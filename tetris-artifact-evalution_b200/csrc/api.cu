@@ -73,11 +73,11 @@ int dispatch(const tetris_filter *f, const float *in, float *out, const ConvShap
   if (f->groups != 1) return launch_depthwise(f, in, out, s, st);
   switch (variant) {
     case TETRIS_VARIANT_GENERIC: return launch_conv_generic(f, in, out, s, st);
-    case TETRIS_VARIANT_TILED: return launch_conv_tiled(f, in, out, s, st);
+    case TETRIS_VARIANT_TILED: return launch_conv_tiled(f, in, out, s, st, false);
     case TETRIS_VARIANT_INTERP: return launch_conv_interp(f, in, out, s, st);
     case TETRIS_VARIANT_TENSOR: return launch_conv_tc(f, in, out, s, st);
     case TETRIS_VARIANT_AUTO:
-      return conv_tiled_supported(f, s) ? launch_conv_tiled(f, in, out, s, st)
+      return conv_tiled_supported(f, s) ? launch_conv_tiled(f, in, out, s, st, true)
                                         : launch_conv_generic(f, in, out, s, st);
     default: set_error("unknown kernel variant %d", variant); return TETRIS_ERR_INVALID;
   }

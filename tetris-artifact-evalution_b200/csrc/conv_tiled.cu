@@ -293,6 +293,7 @@ struct Plan {
   bool valid = false;
   ConvShape shape{};
   int instance = 0;  // which kernel template instance
+  bool use_tc = false;  // automatic choice: the dense tensor-core variant is expected to be faster
   TiledParams p{};
   dim3 grid;
   size_t smem_bytes = 0;
@@ -422,12 +423,22 @@ void fill_plan(const tetris_filter *f, const ConvShape &s, const Candidate &c, i
   plan->instance = c.instance;
 }
 
+// Estimated time (SM clocks) of the dense tensor-core variant: 128 x 128 output tiles, one K step
+// per (filter tap, 32-channel chunk) at about 1700 clocks (measured: 12 tcgen05.mma of
+// 128x128x8 plus operand traffic), plus prologue and epilogue, in waves of one CTA per SM.
+double tc_cost(const tetris_filter *f, const ConvShape &s, int sm_count) {
+  const double tiles = std::ceil((double)s.N * s.OH * s.OW / 128.0 / 0.9) * ((s.OC + 127) / 128);
+  const double iters = (double)s.KS * s.KS * ((s.IC + 31) / 32);
+  return std::ceil(tiles / sm_count) * (iters * 1700.0 + 8000.0);
+}
+
 int make_plan(const tetris_filter *f, const ConvShape &s, Plan *plan) {
   std::vector<Candidate> cands;
   int sm_count = 0;
   const int rc = enumerate_plans(f, s, &sm_count, &cands);
   if (rc) return rc;
   fill_plan(f, s, cands[0], sm_count, plan);
+  plan->use_tc = conv_tc_supported(f, s) && tc_cost(f, s, sm_count) < cands[0].cost;
   return TETRIS_OK;
 }
 
@@ -533,6 +544,24 @@ int tune_conv_tiled(const tetris_filter *f, const float *in, float *out, const C
               c.TH, plan.grid.x, plan.grid.y, plan.smem_bytes, c.cost, ms);
     if (best < 0.f || ms < best) { best = ms; best_plan = plan; }
   }
+  // the dense tensor-core variant competes too, when it covers the shape
+  if (!rc && conv_tc_supported(f, s) && (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
+    rc = launch_conv_tc(f, in, out, s, st);
+    cudaEventRecord(e0, st);
+    for (int i = 0; i < reps && !rc; ++i) rc = launch_conv_tc(f, in, out, s, st);
+    cudaEventRecord(e1, st);
+    if (!rc && cudaEventSynchronize(e1) != cudaSuccess) {
+      set_error("tuning launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+      rc = TETRIS_ERR_CUDA;
+    }
+    if (!rc && !conv_tc_check_error(f)) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, e0, e1);
+      ms /= reps;
+      if (debug) fprintf(stderr, "[tetris tune] tensor-core variant -> %.4f ms\n", ms);
+      if (ms < best) { best = ms; best_plan.use_tc = true; }
+    }
+  }
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
   if (rc) return rc;
@@ -552,7 +581,7 @@ int tune_conv_tiled(const tetris_filter *f, const float *in, float *out, const C
 }
 
 int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
-                      cudaStream_t st) {
+                      cudaStream_t st, bool allow_tc) {
   if (!conv_tiled_supported(f, s)) {
     set_error("tiled kernel does not cover KS=%d stride=%d oc_block=%d tile_ic=%d", s.KS, s.S,
               f->oc_block, f->tile_ic);
@@ -577,6 +606,8 @@ int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const
       cache->last = plan;
     }
   }
+  if (allow_tc && plan.use_tc && (reinterpret_cast<uintptr_t>(in) & 15) == 0)
+    return launch_conv_tc(f, in, out, s, st);
   return launch_plan(plan, in, out, st);
 }
 

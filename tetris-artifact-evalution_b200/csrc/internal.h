@@ -65,8 +65,9 @@ int list_fill(const float *d_filter, int IC, int OC, int KS, int K, int TIC, int
 int launch_conv_generic(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                         cudaStream_t st);
 bool conv_tiled_supported(const tetris_filter *f, const ConvShape &s);
+// allow_tc: let the plan's automatic choice switch to the tensor-core variant
 int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
-                      cudaStream_t st);
+                      cudaStream_t st, bool allow_tc);
 int tune_conv_tiled(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                     cudaStream_t st, int max_candidates, float *best_ms);
 void *tiled_plan_cache_new();
