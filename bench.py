@@ -239,6 +239,12 @@ def main():
             tb.tune_sparse_conv2d(l["f"], l["x"], l["y"], args.batch, L.H, L.W, L.stride, L.pad,
                                   cuda_stream=stream)
 
+    # what the engine's automatic choice is per layer, for the report (after the tuning pass)
+    for l in layers:
+        L = l["L"]
+        l["kernel_variant"] = l["variant"] if l["variant"] != 0 else \
+            tb.auto_choice(l["f"], args.batch, L.H, L.W, L.stride, L.pad)
+
     # ---- device-resident throughput ----
     for _ in range(args.warmup):
         launch_all()
@@ -343,7 +349,8 @@ def main():
         L = l["L"]
         names = {0: "tiled", 1: "generic", 2: "tiled", 3: "interp", 4: "tensor"}
         kind = "depthwise" if L.groups != 1 else (
-            "generic" if l["variant"] == 1 else "%s_%dx%d_s%d" % (names[l["variant"]], L.KS, L.KS, L.stride))
+            "generic" if l["kernel_variant"] == 1 else
+            "%s_%dx%d_s%d" % (names[l["kernel_variant"]], L.KS, L.KS, L.stride))
         t_roof = max(l["bytes"] / (hbm_gbs * 1e9), l["flops"] / fp32_peak)
         per_layer.append({"name": L.name, "kernel": kind, "ms": ms, "nnz": l["nnz"],
                           "gbs": l["bytes"] / (ms * 1e-3) / 1e9,

@@ -150,6 +150,15 @@ int tetris_conv2d_tune(const tetris_filter_t *f, const float *d_input_nhwc, floa
                        int max_candidates, float *best_ms);
 
 /*
+ * Which kernel a TETRIS_VARIANT_AUTO launch of this shape uses at the moment (the tuned choice if
+ * tetris_conv2d_tune ran for the shape, else the cost models'): *variant receives
+ * TETRIS_VARIANT_TILED, _TENSOR or _GENERIC (TETRIS_VARIANT_AUTO for a depthwise filter, which
+ * has a single kernel).  No counterpart in the reference, which has one kernel.
+ */
+int tetris_conv2d_choice(const tetris_filter_t *f, int batch_size, int img_h, int img_w, int stride,
+                         int padding, int *variant);
+
+/*
  * Host NCHW in, host NCHW out, blocking.  Copies the input to the device,
  * transposes it to NHWC there, runs the convolution, transposes back and
  * copies the result out.  The device buffers come from a per-device workspace that

@@ -68,6 +68,7 @@ SIGNATURES = {
     "tetris_conv2d_launch_ex": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I]),
     "tetris_conv2d_time": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _I, _I, _c_float_p]),
     "tetris_conv2d_tune": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _c_float_p]),
+    "tetris_conv2d_choice": (_I, [_VP, _I, _I, _I, _I, _I, _c_int_p]),
     "tetris_conv2d_host": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
     "tetris_conv2d_host_async": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _I]),
     "tetris_host_sync": (_I, [_I, _I]),
@@ -243,6 +244,15 @@ def tune_sparse_conv2d(sparse_filter, input, output, batch_size, img_h, img_w, s
                                     img_w, stride, padding, _stream_ptr(cuda_stream), max_candidates,
                                     ctypes.byref(ms)))
     return ms.value
+
+
+def auto_choice(sparse_filter, batch_size, img_h, img_w, stride, padding):
+    """The variant (VARIANT_TILED / VARIANT_TENSOR / VARIANT_GENERIC, VARIANT_AUTO for depthwise)
+    that an automatic launch of this shape uses at the moment."""
+    v = ctypes.c_int(0)
+    _check(lib().tetris_conv2d_choice(sparse_filter.handle, batch_size, img_h, img_w, stride, padding,
+                                      ctypes.byref(v)))
+    return v.value
 
 
 def cuda_sparse_conv2d(h_input, sparse_filter, batch_size, img_h, img_w, stride, padding,

@@ -409,6 +409,17 @@ int tetris_conv2d_tune(const tetris_filter_t *f, const float *d_input_nhwc, floa
   return tune_conv_tiled(f, d_input_nhwc, d_output_nhwc, s, (cudaStream_t)stream, max_candidates, best_ms);
 }
 
+int tetris_conv2d_choice(const tetris_filter_t *f, int batch_size, int img_h, int img_w, int stride,
+                         int padding, int *variant) {
+  ConvShape s;
+  int rc = make_shape(f, batch_size, img_h, img_w, stride, padding, &s);
+  if (rc) return rc;
+  if (!variant) { set_error("variant pointer is NULL"); return TETRIS_ERR_INVALID; }
+  if (f->groups != 1) { *variant = TETRIS_VARIANT_AUTO; return TETRIS_OK; }  // depthwise: one kernel
+  if (!conv_tiled_supported(f, s)) { *variant = TETRIS_VARIANT_GENERIC; return TETRIS_OK; }
+  return conv_auto_choice(f, s, variant);
+}
+
 int tetris_nchw_to_nhwc(const float *d_src, float *d_dst, int N, int C, int H, int W, void *stream) {
   if (!d_src || !d_dst || N < 0 || C < 1 || H < 1 || W < 1) { set_error("bad layout arguments"); return TETRIS_ERR_INVALID; }
   return launch_nchw_to_nhwc(d_src, d_dst, N, C, H, W, (cudaStream_t)stream);

@@ -37,7 +37,7 @@
 namespace tetris {
 namespace {
 
-constexpr int BM = 128, BN = 128, KC = 32;  // tile: pixels x channels, K chunk (32 floats = 128 B)
+constexpr int BM = 128, KC = 32;  // tile rows (pixels), K chunk (32 floats = 128 B); BN = 64 or 128 channels
 constexpr int kStages = 3;
 constexpr int kTileBytes = BM * KC * 4;     // 16 KiB: one 128-row x 128-byte operand tile
 constexpr int kStageBytes = 4 * kTileBytes; // x, x_lo, w_hi, w_lo
@@ -101,6 +101,7 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_whi,
                const __grid_constant__ CUtensorMap map_wlo, const TcParams p) {
@@ -154,7 +155,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int tap = it / p.n_chunks, chunk = it - tap * p.n_chunks;
         const int r = tap / p.KS, q = tap - r * p.KS;
         unsigned char *st = base + s * kStageBytes;
-        mbar_expect_tx(bar_full(s), x_box_bytes + 2u * kTileBytes);
+        mbar_expect_tx(bar_full(s), x_box_bytes + 2u * (uint32_t)(BN * KC * 4));
         tma_load_4d(smem_u32(st), &map_x, bar_full(s), chunk * KC, w0 + q - p.P, h0 + r - p.P, n0);
         tma_load_3d(smem_u32(st + 2 * kTileBytes), &map_whi, bar_full(s), chunk * KC, oc0, tap);
         tma_load_3d(smem_u32(st + 3 * kTileBytes), &map_wlo, bar_full(s), chunk * KC, oc0, tap);
@@ -296,7 +297,8 @@ struct TcState {
   float *d_hi = nullptr, *d_lo = nullptr;
   int *d_error = nullptr;
   int icp = 0;
-  CUtensorMap map_whi, map_wlo;
+  CUtensorMap map_whi, map_wlo;      // weight tiles of 128 output channels
+  CUtensorMap map_whi64, map_wlo64;  // ... and of 64
   // activation map of the last input pointer / shape
   std::mutex mutex;
   const float *last_in = nullptr;
@@ -304,6 +306,7 @@ struct TcState {
   CUtensorMap map_x;
   TcParams params{};
   dim3 grid;
+  int bn = 128;
 };
 
 }  // namespace
@@ -336,9 +339,11 @@ int conv_tc_prepare(tetris_filter *f, const float *d_dense) {
                                                                                         f->out_channel, f->in_channel, KS, s->icp);
   const cuuint64_t dims[3] = {(cuuint64_t)s->icp, (cuuint64_t)f->out_channel, (cuuint64_t)taps};
   const cuuint64_t strides[2] = {(cuuint64_t)s->icp * 4, (cuuint64_t)s->icp * 4 * f->out_channel};
-  const cuuint32_t box[3] = {KC, BN, 1};
+  const cuuint32_t box[3] = {KC, 128, 1}, box64[3] = {KC, 64, 1};
   if (cudaGetLastError() != cudaSuccess || encode_map(&s->map_whi, s->d_hi, 3, dims, strides, box) ||
-      encode_map(&s->map_wlo, s->d_lo, 3, dims, strides, box)) {
+      encode_map(&s->map_wlo, s->d_lo, 3, dims, strides, box) ||
+      encode_map(&s->map_whi64, s->d_hi, 3, dims, strides, box64) ||
+      encode_map(&s->map_wlo64, s->d_lo, 3, dims, strides, box64)) {
     conv_tc_state_delete(s);
     return TETRIS_OK;
   }
@@ -361,6 +366,7 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
   CUtensorMap map_x;
   TcParams p;
   dim3 grid;
+  int bn = 128;
   {
     std::lock_guard<std::mutex> lock(t->mutex);
     const ConvShape &l = t->last_shape;
@@ -390,13 +396,15 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
       q.tiles_n = (s.N + best_nb - 1) / best_nb;
       q.n_chunks = t->icp / KC;
       q.error_flag = t->d_error;
-      t->grid = dim3((unsigned)(q.tiles_w * q.tiles_h * q.tiles_n), (unsigned)((s.OC + BN - 1) / BN));
+      t->bn = s.OC <= 64 ? 64 : 128;
+      t->grid = dim3((unsigned)(q.tiles_w * q.tiles_h * q.tiles_n), (unsigned)((s.OC + t->bn - 1) / t->bn));
       t->last_in = in;
       t->last_shape = s;
     }
     map_x = t->map_x;
     p = t->params;
     grid = t->grid;
+    bn = t->bn;
   }
   p.out = out;
   const size_t smem = (size_t)kStages * kStageBytes + 1024 + 256;
@@ -404,10 +412,14 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
   int dev = 0;
   TETRIS_CUDA_TRY(cudaGetDevice(&dev));
   if (dev >= 16 || !configured[dev]) {
-    TETRIS_CUDA_TRY(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    TETRIS_CUDA_TRY(cudaFuncSetAttribute(conv_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    TETRIS_CUDA_TRY(cudaFuncSetAttribute(conv_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (dev < 16) configured[dev] = true;
   }
-  conv_tc_kernel<<<grid, kThreads, smem, st>>>(map_x, t->map_whi, t->map_wlo, p);
+  if (bn == 64)
+    conv_tc_kernel<64><<<grid, kThreads, smem, st>>>(map_x, t->map_whi64, t->map_wlo64, p);
+  else
+    conv_tc_kernel<128><<<grid, kThreads, smem, st>>>(map_x, t->map_whi, t->map_wlo, p);
   TETRIS_CUDA_TRY(cudaGetLastError());
   return TETRIS_OK;
 }

@@ -580,6 +580,26 @@ int tune_conv_tiled(const tetris_filter *f, const float *in, float *out, const C
   return TETRIS_OK;
 }
 
+// Which variant an automatic launch of this shape would use right now (tuned plan if there is one,
+// else the cost models): TETRIS_VARIANT_TILED or TETRIS_VARIANT_TENSOR.
+int conv_auto_choice(const tetris_filter *f, const ConvShape &s, int *variant) {
+  Plan plan;
+  PlanCache *cache = static_cast<PlanCache *>(f->plan_cache);
+  bool hit = false;
+  if (cache) {
+    std::lock_guard<std::mutex> lock(cache->mutex);
+    for (const Plan &t : cache->tuned)
+      if (same_shape(t.shape, s)) { plan = t; hit = true; break; }
+    if (!hit && cache->last.valid && same_shape(cache->last.shape, s)) { plan = cache->last; hit = true; }
+  }
+  if (!hit) {
+    const int rc = make_plan(f, s, &plan);
+    if (rc) return rc;
+  }
+  *variant = plan.use_tc ? TETRIS_VARIANT_TENSOR : TETRIS_VARIANT_TILED;
+  return TETRIS_OK;
+}
+
 int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                       cudaStream_t st, bool allow_tc) {
   if (!conv_tiled_supported(f, s)) {

@@ -70,6 +70,7 @@ int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const
                       cudaStream_t st, bool allow_tc);
 int tune_conv_tiled(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                     cudaStream_t st, int max_candidates, float *best_ms);
+int conv_auto_choice(const tetris_filter *f, const ConvShape &s, int *variant);
 void *tiled_plan_cache_new();
 void tiled_plan_cache_delete(void *cache);
 bool conv_interp_supported(const tetris_filter *f, const ConvShape &s);
