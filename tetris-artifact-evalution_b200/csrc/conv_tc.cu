@@ -8,28 +8,52 @@
 // the dense-contraction sub-case the design allows once a profile shows that it pays.  The
 // weights keep their zeros here; sparsity is not exploited, precision is:
 //
-//   x = x_hi + x_lo, w = w_hi + w_lo with *_hi the TF32 truncation (what the tensor core reads
-//   from an FP32 word) and *_lo the remainder; D += x_hi*w_hi + x_lo*w_hi + x_hi*w_lo in FP32
-//   accumulators.  The dropped x_lo*w_lo term is 2^-22 relative; measured error against the CPU
-//   convolution is ~1e-6, inside the 1e-4 bound of the path.
+//   x = x_hi + x_lo, w = w_hi + w_lo with *_hi the value rounded to TF32 and *_lo the rounded
+//   remainder; D += x_hi*w_hi + x_lo*w_hi + x_hi*w_lo in FP32 accumulators.  Rounding to
+//   nearest matters: with the truncation the tensor core applies to a raw FP32 word the
+//   per-product error (up to 3 * 2^-20) has one sign and adds up over the ~5000 products of a
+//   deep layer to more than 1e-4 of a small output; rounded, the error terms (remainder
+//   rounding and the dropped x_lo*w_lo, 2^-22 each) are symmetric and stay near 1e-6.
 //
-// One CTA computes a 128-pixel x 128-channel output tile.  GEMM view: M = pixels of a
-// TW x TH x NB patch, N = output channels, K = (filter tap, 32-channel chunk).  Per K step:
-//   * warp 0 (one thread): TMA tiled loads -- the activation patch shifted by the tap as a 4-D box
-//     of the NHWC tensor (out-of-range coordinates are zero-filled: that is the padding), and the
-//     w_hi / w_lo tiles -- into a 3-stage ring of 128-byte-swizzled shared tiles;
-//   * warps 2-5: derive x_lo = x - trunc_tf32(x) next to the loaded tile (same offsets, so the
-//     swizzle is preserved), publish it to the async proxy;
-//   * warp 1 (one thread): 12 tcgen05.mma (4 K-slices x 3 passes) into the TMEM accumulator,
-//     then tcgen05.commit frees the stage.
-// Epilogue: warps 2-5 read their TMEM lane quarter (tcgen05.ld) and store 512 contiguous bytes per
-// pixel (NHWC).  Every barrier wait is bounded: on a timeout an error flag is raised, all roles
-// drain, TMEM is freed and the kernel returns; the host reports TETRIS_ERR_CUDA.
+// The tensor core adds into its FP32 accumulator with truncation, so a long accumulation chain
+// drifts toward zero (measured: 5e-5 absolute on outputs of 0.1 after the 1700 accumulation
+// steps of a 512-channel 3x3 layer).  The chain is therefore cut: the tensor core accumulates
+// two K steps (24 MMAs) from zero into a partial accumulator, and CUDA-core warps add the
+// partial to the running sum, kept in registers, with round-to-nearest FP32 adds.
+//
+// A persistent CTA (one per SM) walks 128-pixel x 128-channel (or x 64) output tiles.  GEMM
+// view: M = pixels of a TW x TH x NB tile, N = output channels, K = (32-channel chunk, filter
+// tap).  The M-side operand is fed to the tensor core from TENSOR MEMORY, the N-side operand
+// from shared memory.  Every hand-over has its own ring with a full/empty barrier pair, so the
+// roles run decoupled (measured: with one shared ring the barrier round trips, not the tensor
+// pipe, set the pace):
+//   * warp 0 (one thread): one TMA load per 32-channel chunk of the tile's pixels WITH THEIR
+//     HALO -- a 4-D box (32 channels, TW+KS-1, TH+KS-1, NB) of the NHWC tensor; out-of-range
+//     coordinates are zero-filled, which is the padding -- into a 2-deep ring of
+//     128-byte-swizzled stages.  All KS*KS taps read their shifted rows from the one patch:
+//     a box per tap moves 6x the bytes, and 128-byte rows scattered over L2 come in at only
+//     ~25 B/clock/SM (measured), which made the activation loads as slow as the MMAs;
+//   * warp 2 (one thread): one bulk copy per K step of a prepared {w_hi, w_lo} tile image into
+//     a 5-deep ring;
+//   * warps 4-11: per K step read the patch rows of the tap (un-swizzling) and write
+//     x_hi = tf32(x) and x_lo = tf32(x - x_hi) into a 4-deep ring of 64 TMEM columns
+//     (tcgen05.st); they also do the waiting for the MMA warp (weights landed, partial
+//     accumulator drained);
+//   * warp 1 (converged, one elected lane issues): 12 tcgen05.mma per K step (4 K-slices x 3
+//     passes) into one of two partial accumulators in TMEM; after every second K step one
+//     tcgen05.commit hands the partial accumulator over and releases the operand stages;
+//   * warps 12-19: read the partial accumulator (tcgen05.ld; a warp may touch the TMEM lanes
+//     of its quarter, two warps share a quarter and take half of the channels each), release
+//     it, add it to the running sum; after the tile's last K step store the sums, 256
+//     contiguous bytes per thread (NHWC).
+// Every barrier wait is bounded: on a timeout an error flag is raised, all roles drain, TMEM is
+// freed and the kernel returns; the host reports TETRIS_ERR_CUDA.
 //
 // No cluster launch, no multicast.  Covers stride 1, IC % 4 == 0 (TMA needs 16-byte strides).
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "internal.h"
@@ -38,19 +62,30 @@ namespace tetris {
 namespace {
 
 constexpr int BM = 128, KC = 32;  // tile rows (pixels), K chunk (32 floats = 128 B); BN = 64 or 128 channels
-constexpr int kStages = 3;
+constexpr int kXStages = 2;                 // ring of activation tiles (shared memory, TMA target)
+constexpr int kWStages = 5;                 // ring of {w_hi, w_lo} tile pairs (shared memory, TMA target)
+constexpr int kAStages = 4;                 // ring of {x, x_lo} operand blocks (tensor memory)
 constexpr int kTileBytes = BM * KC * 4;     // 16 KiB: one 128-row x 128-byte operand tile
-constexpr int kStageBytes = 4 * kTileBytes; // x, x_lo, w_hi, w_lo
-constexpr int kThreads = 192;               // warp 0 producer, warp 1 MMA, warps 2-5 convert + epilogue
+constexpr int kPatchRows = 256;             // rows of 128 bytes an activation stage holds
+constexpr int kPatchBytes = kPatchRows * KC * 4;
+constexpr int kSmemTiles = kXStages * kPatchBytes + kWStages * 2 * kTileBytes;
+constexpr int kPromote = 2;                 // K steps accumulated on the tensor core before the FP32 add outside
+constexpr int kTmemCols = 512;              // 2 partial accumulators (<= 128 columns each) + 4 x 64 operand columns
+constexpr int kTmemA = 256;                 // first operand column
+constexpr int kGroups = 4;                  // "group done" barriers in rotation (a group = kPromote K steps)
+constexpr int kThreads = 640;               // warp 0 x loads, 1 MMA, 2 w loads, 4-11 convert, 12-19 sum + store
+constexpr int kNumBars = 2 * kXStages + kWStages + kAStages + kGroups + 2;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct TcParams {
   float *out;
   int N, OH, OW, OC, P, KS;
-  int TW, TH, NB;              // pixel patch of a tile: TW x TH x NB <= 128 rows
+  int TW, TH, NB;              // pixels of a tile: TW x TH x NB <= 128 rows
+  int PW, PH;                  // the tile with its halo: PW = TW + KS - 1, PH = TH + KS - 1
   int tiles_w, tiles_h, tiles_n;
   int n_chunks;                // ceil(IC / 32)
   int *error_flag;
+  const float *w_tiles;        // weight tile images, see tc_weight_tiles_kernel
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -81,54 +116,90 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   *abort_flag = 1;
   return false;
 }
+// The same for a whole converged warp, with one answer for all lanes.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int lane) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3) {
   asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 // K-major operand tile, 128-byte rows, 128B swizzle, 8-row atoms 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
   return (uint64_t)((saddr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
-               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// FP32 -> TF32 (10 mantissa bits), round to nearest, ties away from zero; low 13 bits are zero.
+// Integer form of cvt.rna.tf32.f32 for finite inputs (the conversion pipe runs at a quarter of
+// the integer rate, and the converter warps round 64 values per K step each).
+__device__ __forceinline__ uint32_t round_tf32(float v) { return (__float_as_uint(v) + 0x1000u) & 0xFFFFE000u; }
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+  return pred != 0;
+}
+// A-operand-in-TMEM form: D[tmem] (+)= A[tmem] * B[smem descriptor].
+// The shared-memory descriptor is passed as its two words: the high word is a constant, the low
+// word is the start address field plus a constant, so that stepping along K or to the w_lo tile
+// is one integer add (the MMA thread's own instruction count is what limits the issue rate).
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t db_lo, uint32_t db_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\n.reg .b64 d;\nmov.b64 d, {%2, %3};\nsetp.ne.b32 p, %5, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], d, %4, p;\n}"
+               ::"r"(tmem_d), "r"(tmem_a), "r"(db_lo), "r"(db_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_whi,
-               const __grid_constant__ CUtensorMap map_wlo, const TcParams p) {
+conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char *base = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(base + kStages * kStageBytes);
-  // barriers: full[s], conv[s], empty[s], accum
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kStages + 1);
+  unsigned char *xbase = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+  unsigned char *wbase = xbase + kXStages * kPatchBytes;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(xbase + kSmemTiles);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  auto bar_full = [&](int s) { return smem_u32(&bars[s]); };
-  auto bar_conv = [&](int s) { return smem_u32(&bars[kStages + s]); };
-  auto bar_empty = [&](int s) { return smem_u32(&bars[2 * kStages + s]); };
-  const uint32_t bar_accum = smem_u32(&bars[3 * kStages]);
+  auto bar_xfull = [&](int s) { return smem_u32(&bars[s]); };
+  auto bar_xempty = [&](int s) { return smem_u32(&bars[kXStages + s]); };
+  auto bar_wfull = [&](int s) { return smem_u32(&bars[2 * kXStages + s]); };
+  auto bar_afull = [&](int s) { return smem_u32(&bars[2 * kXStages + kWStages + s]); };
+  auto bar_gdone = [&](int c) { return smem_u32(&bars[2 * kXStages + kWStages + kAStages + c]); };
+  auto bar_pempty = [&](int b) { return smem_u32(&bars[kNumBars - 2 + b]); };
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar_full(s), 1);
-      mbar_init(bar_conv(s), 4);
-      mbar_init(bar_empty(s), 1);
-    }
-    mbar_init(bar_accum, 1);
+    for (int s = 0; s < kXStages; ++s) { mbar_init(bar_xfull(s), 1); mbar_init(bar_xempty(s), 8); }
+    for (int s = 0; s < kWStages; ++s) mbar_init(bar_wfull(s), 1);
+    for (int s = 0; s < kAStages; ++s) mbar_init(bar_afull(s), 4);
+    for (int c = 0; c < kGroups; ++c) mbar_init(bar_gdone(c), 1);
+    for (int b = 0; b < 2; ++b) mbar_init(bar_pempty(b), 8);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+  if (warp == 1) {  // the whole tensor memory of the SM: this kernel runs one CTA per SM
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -136,133 +207,243 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  // ---- which tile ----
-  int bx = blockIdx.x;
-  const int tw = bx % p.tiles_w; bx /= p.tiles_w;
-  const int th = bx % p.tiles_h;
-  const int tn = bx / p.tiles_h;
-  const int w0 = tw * p.TW, h0 = th * p.TH, n0 = tn * p.NB;
-  const int oc0 = blockIdx.y * BN;
+  // Persistent CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the channel tile is the
+  // fastest index, so CTAs that run side by side read the same activation patch.
   const int taps = p.KS * p.KS;
-  const int iters = taps * p.n_chunks;
-  const uint32_t x_box_bytes = (uint32_t)(p.TW * p.TH * p.NB * KC * 4);
+  const int iters = taps * p.n_chunks;                      // K steps of a tile
+  const int tile_groups = (iters + kPromote - 1) / kPromote;  // groups of a tile
+  const int oc_tiles = (p.OC + BN - 1) / BN;
+  const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_n * oc_tiles;
+  auto decode = [&](int t, int &w0, int &h0, int &n0, int &oc0) {
+    oc0 = (t % oc_tiles) * BN; t /= oc_tiles;
+    w0 = (t % p.tiles_w) * p.TW; t /= p.tiles_w;
+    h0 = (t % p.tiles_h) * p.TH;
+    n0 = (t / p.tiles_h) * p.NB;
+  };
+  // One tcgen05.commit per group tells everyone that the group's MMAs have completed: the
+  // summing warps take the partial accumulator, the weight loader and the converters reuse
+  // the operand stages those MMAs read.  (A commit costs the issuing thread 150-200 clocks,
+  // measured, so there is one per two K steps rather than two per K step.)  K step g of this
+  // CTA (counted across tiles) lies in group group_of(g); a stage last used by step g - depth
+  // is free once that group is done.
+  auto group_of = [&](int g) { const int j = g / iters; return j * tile_groups + (g - j * iters) / kPromote; };
+  auto wait_group = [&](int c) { return mbar_wait(bar_gdone(c % kGroups), (c / kGroups) & 1, abort_flag); };
+  auto wait_group_warp = [&](int c) { return mbar_wait_warp(bar_gdone(c % kGroups), (c / kGroups) & 1, abort_flag, lane); };
 
   if (warp == 0) {
+    // ---- activation loads ----
     if (lane == 0) {
-      for (int it = 0; it < iters; ++it) {
-        const int s = it % kStages;
-        if (!mbar_wait(bar_empty(s), ((it / kStages) & 1) ^ 1, abort_flag)) break;
-        const int tap = it / p.n_chunks, chunk = it - tap * p.n_chunks;
-        const int r = tap / p.KS, q = tap - r * p.KS;
-        unsigned char *st = base + s * kStageBytes;
-        mbar_expect_tx(bar_full(s), x_box_bytes + 2u * (uint32_t)(BN * KC * 4));
-        tma_load_4d(smem_u32(st), &map_x, bar_full(s), chunk * KC, w0 + q - p.P, h0 + r - p.P, n0);
-        tma_load_3d(smem_u32(st + 2 * kTileBytes), &map_whi, bar_full(s), chunk * KC, oc0, tap);
-        tma_load_3d(smem_u32(st + 3 * kTileBytes), &map_wlo, bar_full(s), chunk * KC, oc0, tap);
+      // One patch per 32-channel chunk: the tile plus its halo, shared by all taps.
+      const uint32_t x_box_bytes = (uint32_t)(p.PW * p.PH * p.NB * KC * 4);
+      int u = 0;  // patch count of this CTA, across tiles
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int w0, h0, n0, oc0;
+        decode(t, w0, h0, n0, oc0);
+        for (int chunk = 0; chunk < p.n_chunks; ++chunk, ++u) {
+          const int s = u % kXStages;
+          if (!(ok = mbar_wait(bar_xempty(s), ((u / kXStages) & 1) ^ 1, abort_flag))) break;
+          mbar_expect_tx(bar_xfull(s), x_box_bytes);
+          tma_load_4d(smem_u32(xbase + s * kPatchBytes), &map_x, bar_xfull(s), chunk * KC, w0 - p.P, h0 - p.P, n0);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ---- weight loads ----
+    if (lane == 0) {
+      int g = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int w0, h0, n0, oc0;
+        decode(t, w0, h0, n0, oc0);
+        for (int it = 0; it < iters; ++it, ++g) {
+          const int s = g % kWStages;
+          if (g >= kWStages && !(ok = wait_group(group_of(g - kWStages)))) break;
+          // K step `it` of channel tile oc0 / BN: one contiguous {w_hi, w_lo} image
+          const float *src = p.w_tiles + ((size_t)it * oc_tiles + oc0 / BN) * (2 * BN * KC);
+          mbar_expect_tx(bar_wfull(s), (uint32_t)(2 * BN * KC * 4));
+          bulk_load(smem_u32(wbase + s * 2 * kTileBytes), src, (uint32_t)(2 * BN * KC * 4), bar_wfull(s));
+        }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-      bool ok = true;
-      for (int it = 0; it < iters && ok; ++it) {
-        const int s = it % kStages;
-        const uint32_t parity = (it / kStages) & 1;
-        ok = mbar_wait(bar_full(s), parity, abort_flag) && mbar_wait(bar_conv(s), parity, abort_flag);
-        if (!ok) break;
+    // ---- MMA issue.  The whole warp runs the loop converged and one elected lane issues, so
+    //      that descriptors, addresses and the instruction descriptor stay in uniform registers
+    //      (with a single lane of a diverged warp every MMA pays for moving its operands there,
+    //      and the issuing thread, not the tensor pipe, sets the pace). ----
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    int g = 0, c = 0;  // K step and group of this CTA, counted across tiles
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int it0 = 0; it0 < iters && ok; it0 += kPromote, ++c) {
+        const int b = c & 1;
+        // (the converters have also waited for the summing warps to drain this partial accumulator)
+        const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
+        const int it1 = min(it0 + kPromote, iters);
+        for (int it = it0; it < it1; ++it, ++g) {
+          const int sw = g % kWStages, sa = g % kAStages;
+          // one wait per K step: afull stands for all inputs of the step (see the converters)
+          if (!(ok = mbar_wait_warp(bar_afull(sa), (g / kAStages) & 1, abort_flag, lane))) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t dw = umma_desc(smem_u32(wbase + sw * 2 * kTileBytes));
+          const uint32_t dlo = (uint32_t)dw, dhi = (uint32_t)(dw >> 32);
+          const uint32_t ta = tmem_base + (uint32_t)(kTmemA + sa * 2 * KC);
+          if (elect_one()) {
+#pragma unroll
+            for (int k = 0; k < KC / 8; ++k) {  // 32 bytes along K = 2 in the address field; w_lo follows w_hi
+              umma_tf32_ts(tmem_d, ta + k * 8, dlo + 2 * k, dhi, idesc, (it > it0 || k) ? 1u : 0u);
+              umma_tf32_ts(tmem_d, ta + KC + k * 8, dlo + 2 * k, dhi, idesc, 1u);
+              umma_tf32_ts(tmem_d, ta + k * 8, dlo + 2 * k + (BN * KC * 4 >> 4), dhi, idesc, 1u);
+            }
+          }
+          __syncwarp();
+        }
+        if (ok && elect_one()) umma_commit(bar_gdone(c % kGroups));  // arrives when the group's last MMA has completed
+        __syncwarp();
+      }
+    }
+  } else if (warp >= 4 && warp < 12) {
+    // ---- warps 4..11: shared activation tile -> {x_hi, x_lo} in tensor memory.  A warp may
+    //      touch only the TMEM lanes of its quarter (warp % 4); two warps share a quarter and
+    //      take 16 of the 32 K columns each.  Row r keeps its 16-byte chunk c at c ^ (r & 7).
+    //      Every warp handles every K step, in order: a parity wait cannot tell phase n from
+    //      phase n + 2, so no warp may run a whole ring ahead of another.
+    const int quarter = warp & 3, set = (warp - 4) >> 2;
+    const int row = quarter * 32 + lane;
+    // patch row of this thread's pixel for tap (0, 0); rows past the tile read row 0
+    const int pw = row % p.TW, ph = (row / p.TW) % p.TH, pn = row / (p.TW * p.TH);
+    const int prow0 = pn < p.NB ? (pn * p.PH + ph) * p.PW + pw : 0;
+    const bool live = pn < p.NB;
+    int g = 0, u = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int it = 0; it < iters; ++it, ++g) {
+        const int chunk = it / taps, tap = it - chunk * taps;
+        const int sx = u % kXStages, sa = g % kAStages;
+        const bool last_of_chunk = tap == taps - 1;
+        if ((g & 1) == set) {
+          // The MMA warp waits for afull only (a wait costs it ~150 clocks in which nothing is
+          // issued, and the tensor pipe holds only ~250 clocks of queued work), so afull stands
+          // for everything the MMAs of this K step need: the weights have landed and, at the
+          // first K step of a group, the summing warps have drained the partial accumulator
+          // the group adds into (two groups ago) ...
+          if (!(ok = mbar_wait_warp(bar_wfull(g % kWStages), (g / kWStages) & 1, abort_flag, lane))) break;
+          if (it % kPromote == 0) {
+            const int c = group_of(g);
+            if (!(ok = mbar_wait_warp(bar_pempty(c & 1), ((c >> 1) & 1) ^ 1, abort_flag, lane))) break;
+          }
+          // ... and the MMAs that read this operand stage four K steps ago have completed.
+          if (g >= kAStages && !(ok = wait_group_warp(group_of(g - kAStages)))) break;
+          if (!(ok = mbar_wait_warp(bar_xfull(sx), (u / kXStages) & 1, abort_flag, lane))) break;
+          const int r = tap / p.KS, q = tap - r * p.KS;
+          const int prow = live ? prow0 + r * p.PW + q : 0;
+          const unsigned char *src = xbase + sx * kPatchBytes + prow * 128;
+          uint32_t hi[32], lo[32];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(src + ((c ^ (prow & 7)) << 4));
+            hi[4 * c + 0] = v.x; hi[4 * c + 1] = v.y; hi[4 * c + 2] = v.z; hi[4 * c + 3] = v.w;
+          }
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const float v = __uint_as_float(hi[c]);
+            hi[c] = round_tf32(v);
+            lo[c] = round_tf32(v - __uint_as_float(hi[c]));
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(kTmemA + sa * 2 * KC);
+          tmem_st32(taddr, hi);
+          tmem_st32(taddr + KC, lo);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_afull(sa));
+        }
+        // The patch is released by every warp once its own last K step of the chunk is behind
+        // the tensor-memory store.  (Releasing a stage right after the loads, ahead of long
+        // waits, produced wrong results on the 56x56 and 112x112 layers.)
+        if (last_of_chunk) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_xempty(sx));
+          ++u;
+        }
+      }
+    }
+  } else if (warp >= 12) {
+    // ---- warps 12..19: running sum in registers, store at the end of the tile ----
+    constexpr int NC = BN / 2;             // channels per thread
+    const int quarter = warp & 3, half = (warp - 12) >> 2;
+    const int row = quarter * 32 + lane;   // tile row = pixel = TMEM lane
+    const int pw = row % p.TW, ph = (row / p.TW) % p.TH, pn = row / (p.TW * p.TH);
+    const bool vec = (p.OC & 3) == 0;
+    int c = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      float acc[NC];
+#pragma unroll
+      for (int j = 0; j < NC; ++j) acc[j] = 0.f;
+      for (int it0 = 0; it0 < iters; it0 += kPromote, ++c) {
+        const int b = c & 1;
+        if (!(ok = wait_group_warp(c))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t st = smem_u32(base + s * kStageBytes);
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + half * NC);
 #pragma unroll
-        for (int k = 0; k < KC / 8; ++k) {
-          const uint64_t dx = umma_desc(st + k * 32), dxl = umma_desc(st + kTileBytes + k * 32);
-          const uint64_t dwh = umma_desc(st + 2 * kTileBytes + k * 32), dwl = umma_desc(st + 3 * kTileBytes + k * 32);
-          umma_tf32(tmem_base, dx, dwh, idesc, (it | k) ? 1u : 0u);
-          umma_tf32(tmem_base, dxl, dwh, idesc, 1u);
-          umma_tf32(tmem_base, dx, dwl, idesc, 1u);
+        for (int c0 = 0; c0 < NC; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld16(taddr + c0, v);
+          if (c0 + 16 == NC) {  // everything is in registers: the tensor core may overwrite the partial
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_pempty(b));
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[c0 + j] += __uint_as_float(v[j]);
         }
-        umma_commit(bar_empty(s));  // the stage may be refilled once these MMAs have read it
       }
-      umma_commit(bar_accum);       // arrives when everything issued so far has completed
-    }
-  } else {
-    // ---- warps 2..5: x_lo for every landed stage, then the epilogue ----
-    const int ct = tid - 64;  // 0..127: the tile row this thread converts
-    for (int it = 0; it < iters; ++it) {
-      const int s = it % kStages;
-      if (!mbar_wait(bar_full(s), (it / kStages) & 1, abort_flag)) break;
-      const float4 *src = reinterpret_cast<const float4 *>(base + s * kStageBytes + ct * 128);
-      float4 *dst = reinterpret_cast<float4 *>(base + s * kStageBytes + kTileBytes + ct * 128);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int jj = (j + lane) & 7;  // spread the lanes of a warp over the banks
-        const float4 v = src[jj];
-        float4 lo;
-        lo.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
-        lo.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
-        lo.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
-        lo.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-        dst[jj] = lo;
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_conv(s));
-    }
-    const bool done = mbar_wait(bar_accum, 0, abort_flag);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (done && !*abort_flag) {
-      const int quarter = warp & 3;          // TMEM lanes this warp may read
-      const int row = quarter * 32 + lane;   // tile row = pixel
-      const int pw = row % p.TW, ph = (row / p.TW) % p.TH, pn = row / (p.TW * p.TH);
+      if (!ok) break;
+      int w0, h0, n0, oc0;
+      decode(t, w0, h0, n0, oc0);
       const int ow = w0 + pw, oh = h0 + ph, n = n0 + pn;
-      const bool row_ok = pn < p.NB && ow < p.OW && oh < p.OH && n < p.N;
-      float *o = p.out + (((size_t)n * p.OH + oh) * p.OW + ow) * p.OC + oc0;
-      const bool vec = (p.OC & 3) == 0;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t v[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-            "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-              "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-              "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-            : "r"(taddr));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (!row_ok) continue;
-        if (vec && oc0 + c0 + 32 <= p.OC) {
+      if (!(pn < p.NB && ow < p.OW && oh < p.OH && n < p.N) || *abort_flag) continue;
+      const int ocb = oc0 + half * NC;
+      float *o = p.out + (((size_t)n * p.OH + oh) * p.OW + ow) * p.OC + ocb;
+      if (vec && ocb + NC <= p.OC) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<float4 *>(o + c0 + j) =
-                make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-        } else {
+        for (int j = 0; j < NC; j += 4) *reinterpret_cast<float4 *>(o + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (oc0 + c0 + j < p.OC) o[c0 + j] = __uint_as_float(v[j]);
-        }
+        for (int j = 0; j < NC; ++j)
+          if (ocb + j < p.OC) o[j] = acc[j];
       }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (tid == 0 && *abort_flag) atomicExch(p.error_flag, 1);
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
-// Dense OIHW -> [tap][OC][ICP] in two FP32 tensors: the weight itself (the tensor core reads its
-// TF32 truncation) and the remainder w - trunc(w).
-__global__ void tc_weight_split_kernel(const float *__restrict__ filt, float *__restrict__ hi, float *__restrict__ lo,
-                                       int OC, int IC, int KS, int ICP) {
-  const long long total = (long long)KS * KS * OC * ICP;
+// Dense OIHW -> the images the weight loader copies: for every (32-channel chunk, tap, channel
+// tile) a block {w_hi, w_lo} of BN rows x 128 bytes each, rows = output channels, already in the
+// 128-byte-swizzled order the tensor core reads (16-byte chunk j of row r sits at chunk
+// j ^ (r & 7)), so that one contiguous bulk copy fills a stage.  Channels past IC or OC are zero.
+__global__ void tc_weight_tiles_kernel(const float *__restrict__ filt, float *__restrict__ tiles,
+                                       int OC, int IC, int KS, int n_chunks, int oc_tiles, int BN) {
+  const long long total = (long long)KS * KS * n_chunks * oc_tiles * 2 * BN * KC;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int ic = (int)(i % ICP);
-    const int oc = (int)((i / ICP) % OC);
-    const int tap = (int)(i / ((long long)ICP * OC));
+    const int col = (int)(i % KC);
+    const int row = (int)((i / KC) % BN);
+    const int half = (int)((i / ((long long)KC * BN)) % 2);
+    long long tile = i / ((long long)2 * KC * BN);
+    const int oct = (int)(tile % oc_tiles); tile /= oc_tiles;
+    const int tap = (int)(tile % (KS * KS));  // K steps run chunk-major, tap-minor
+    const int chunk = (int)(tile / (KS * KS));
+    const int k = (((col >> 2) ^ (row & 7)) << 2) | (col & 3);
+    const int ic = chunk * KC + k, oc = oct * BN + row;
     float w = 0.f;
-    if (ic < IC) w = filt[((size_t)oc * IC + ic) * KS * KS + tap];
-    hi[i] = w;
-    lo[i] = w - __uint_as_float(__float_as_uint(w) & 0xFFFFE000u);
+    if (ic < IC && oc < OC) w = filt[((size_t)oc * IC + ic) * KS * KS + tap];
+    const float h = __uint_as_float(round_tf32(w));
+    tiles[i] = half ? __uint_as_float(round_tf32(w - h)) : h;
   }
 }
 
@@ -294,11 +475,9 @@ int encode_map(CUtensorMap *map, void *ptr, int rank, const cuuint64_t *dims, co
 }
 
 struct TcState {
-  float *d_hi = nullptr, *d_lo = nullptr;
+  float *d_tiles = nullptr;  // weight tile images
   int *d_error = nullptr;
-  int icp = 0;
-  CUtensorMap map_whi, map_wlo;      // weight tiles of 128 output channels
-  CUtensorMap map_whi64, map_wlo64;  // ... and of 64
+  int n_chunks = 0, bn = 128;  // K chunks per tap; channel tile (fixed by the filter: 64 up to 64 channels)
   // activation map of the last input pointer / shape
   std::mutex mutex;
   const float *last_in = nullptr;
@@ -306,7 +485,6 @@ struct TcState {
   CUtensorMap map_x;
   TcParams params{};
   dim3 grid;
-  int bn = 128;
 };
 
 }  // namespace
@@ -314,7 +492,7 @@ struct TcState {
 void conv_tc_state_delete(void *state) {
   TcState *s = static_cast<TcState *>(state);
   if (!s) return;
-  cudaFree(s->d_hi); cudaFree(s->d_lo); cudaFree(s->d_error);
+  cudaFree(s->d_tiles); cudaFree(s->d_error);
   delete s;
 }
 
@@ -326,24 +504,19 @@ int conv_tc_prepare(tetris_filter *f, const float *d_dense) {
   TcState *s = new (std::nothrow) TcState();
   if (!s) return TETRIS_OK;
   const int KS = f->kernel_size, taps = KS * KS;
-  s->icp = (f->in_channel + KC - 1) / KC * KC;
-  const size_t elems = (size_t)taps * f->out_channel * s->icp;
-  if (cudaMalloc(&s->d_hi, elems * 4) != cudaSuccess || cudaMalloc(&s->d_lo, elems * 4) != cudaSuccess ||
-      cudaMalloc(&s->d_error, sizeof(int)) != cudaSuccess) {
+  s->n_chunks = (f->in_channel + KC - 1) / KC;
+  s->bn = f->out_channel <= 64 ? 64 : 128;
+  const int oc_tiles = (f->out_channel + s->bn - 1) / s->bn;
+  const size_t elems = (size_t)taps * s->n_chunks * oc_tiles * 2 * s->bn * KC;
+  if (cudaMalloc(&s->d_tiles, elems * 4) != cudaSuccess || cudaMalloc(&s->d_error, sizeof(int)) != cudaSuccess) {
     cudaGetLastError();
     conv_tc_state_delete(s);
     return TETRIS_OK;
   }
   cudaMemset(s->d_error, 0, sizeof(int));
-  tc_weight_split_kernel<<<(unsigned)std::min<size_t>((elems + 255) / 256, 4096), 256>>>(d_dense, s->d_hi, s->d_lo,
-                                                                                        f->out_channel, f->in_channel, KS, s->icp);
-  const cuuint64_t dims[3] = {(cuuint64_t)s->icp, (cuuint64_t)f->out_channel, (cuuint64_t)taps};
-  const cuuint64_t strides[2] = {(cuuint64_t)s->icp * 4, (cuuint64_t)s->icp * 4 * f->out_channel};
-  const cuuint32_t box[3] = {KC, 128, 1}, box64[3] = {KC, 64, 1};
-  if (cudaGetLastError() != cudaSuccess || encode_map(&s->map_whi, s->d_hi, 3, dims, strides, box) ||
-      encode_map(&s->map_wlo, s->d_lo, 3, dims, strides, box) ||
-      encode_map(&s->map_whi64, s->d_hi, 3, dims, strides, box64) ||
-      encode_map(&s->map_wlo64, s->d_lo, 3, dims, strides, box64)) {
+  tc_weight_tiles_kernel<<<(unsigned)std::min<size_t>((elems + 255) / 256, 4096), 256>>>(
+      d_dense, s->d_tiles, f->out_channel, f->in_channel, KS, s->n_chunks, oc_tiles, s->bn);
+  if (cudaGetLastError() != cudaSuccess) {
     conv_tc_state_delete(s);
     return TETRIS_OK;
   }
@@ -372,32 +545,45 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
     const ConvShape &l = t->last_shape;
     const bool hit = t->last_in == in && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S;
     if (!hit) {
-      // pixel patch: TW x TH x NB rows, at most 128, as full as possible
-      int best_tw = 1, best_th = 1, best_nb = 1;
+      // pixels of a tile: TW x TH x NB rows, at most 128, as full as possible, and such that
+      // the tile with its halo fits an activation stage
+      int best_tw = 0, best_th = 1, best_nb = 1;
       double best = -1.0;
       for (int TW = 1; TW <= std::min(s.OW, 128); ++TW) {
-        const int TH = std::min(s.OH, 128 / TW);
-        if (TH < 1) continue;
-        const int NB = (TH == s.OH && TW == s.OW) ? std::min(s.N, 128 / (TW * TH)) : 1;
+        int TH = std::min(s.OH, 128 / TW);
+        while (TH > 1 && (TW + s.KS - 1) * (TH + s.KS - 1) > kPatchRows) --TH;
+        if (TH < 1 || (TW + s.KS - 1) * (TH + s.KS - 1) > kPatchRows) continue;
+        int NB = (TH == s.OH && TW == s.OW) ? std::min(s.N, 128 / (TW * TH)) : 1;
+        while (NB > 1 && (TW + s.KS - 1) * (TH + s.KS - 1) * NB > kPatchRows) --NB;
         const double tiles = (double)((s.OW + TW - 1) / TW) * ((s.OH + TH - 1) / TH) * ((s.N + NB - 1) / NB);
         const double eff = (double)s.N * s.OH * s.OW / (tiles * 128.0);
         if (eff > best) { best = eff; best_tw = TW; best_th = TH; best_nb = NB; }
       }
+      if (best_tw == 0) {
+        set_error("tensor-core variant: no tile of this layer fits an activation stage with its halo");
+        return TETRIS_ERR_UNSUPPORTED;
+      }
+      const int PW = best_tw + s.KS - 1, PH = best_th + s.KS - 1;
       const cuuint64_t dims[4] = {(cuuint64_t)s.IC, (cuuint64_t)s.W, (cuuint64_t)s.H, (cuuint64_t)s.N};
       const cuuint64_t strides[3] = {(cuuint64_t)s.IC * 4, (cuuint64_t)s.IC * 4 * s.W, (cuuint64_t)s.IC * 4 * s.W * s.H};
-      const cuuint32_t box[4] = {KC, (cuuint32_t)best_tw, (cuuint32_t)best_th, (cuuint32_t)best_nb};
+      const cuuint32_t box[4] = {KC, (cuuint32_t)PW, (cuuint32_t)PH, (cuuint32_t)best_nb};
       const int rc = encode_map(&t->map_x, const_cast<float *>(in), 4, dims, strides, box);
       if (rc) return rc;
       TcParams &q = t->params;
       q.N = s.N; q.OH = s.OH; q.OW = s.OW; q.OC = s.OC; q.P = s.P; q.KS = s.KS;
       q.TW = best_tw; q.TH = best_th; q.NB = best_nb;
+      q.PW = PW; q.PH = PH;
       q.tiles_w = (s.OW + best_tw - 1) / best_tw;
       q.tiles_h = (s.OH + best_th - 1) / best_th;
       q.tiles_n = (s.N + best_nb - 1) / best_nb;
-      q.n_chunks = t->icp / KC;
+      q.n_chunks = t->n_chunks;
+      q.w_tiles = t->d_tiles;
       q.error_flag = t->d_error;
-      t->bn = s.OC <= 64 ? 64 : 128;
-      t->grid = dim3((unsigned)(q.tiles_w * q.tiles_h * q.tiles_n), (unsigned)((s.OC + t->bn - 1) / t->bn));
+      int dev = 0, sms = 0;
+      TETRIS_CUDA_TRY(cudaGetDevice(&dev));
+      TETRIS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      const long long total = (long long)q.tiles_w * q.tiles_h * q.tiles_n * ((s.OC + t->bn - 1) / t->bn);
+      t->grid = dim3((unsigned)std::min<long long>(total, sms));  // persistent: one CTA per SM
       t->last_in = in;
       t->last_shape = s;
     }
@@ -407,7 +593,7 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
     bn = t->bn;
   }
   p.out = out;
-  const size_t smem = (size_t)kStages * kStageBytes + 1024 + 256;
+  const size_t smem = (size_t)kSmemTiles + 1024 + kNumBars * 8 + 16;
   static thread_local bool configured[16] = {false};
   int dev = 0;
   TETRIS_CUDA_TRY(cudaGetDevice(&dev));
@@ -417,9 +603,9 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
     if (dev < 16) configured[dev] = true;
   }
   if (bn == 64)
-    conv_tc_kernel<64><<<grid, kThreads, smem, st>>>(map_x, t->map_whi64, t->map_wlo64, p);
+    conv_tc_kernel<64><<<grid, kThreads, smem, st>>>(map_x, p);
   else
-    conv_tc_kernel<128><<<grid, kThreads, smem, st>>>(map_x, t->map_whi, t->map_wlo, p);
+    conv_tc_kernel<128><<<grid, kThreads, smem, st>>>(map_x, p);
   TETRIS_CUDA_TRY(cudaGetLastError());
   return TETRIS_OK;
 }
