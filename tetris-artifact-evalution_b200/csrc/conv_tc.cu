@@ -18,8 +18,9 @@
 // The tensor core adds into its FP32 accumulator with truncation, so a long accumulation chain
 // drifts toward zero (measured: 5e-5 absolute on outputs of 0.1 after the 1700 accumulation
 // steps of a 512-channel 3x3 layer).  The chain is therefore cut: the tensor core accumulates
-// two K steps (24 MMAs) from zero into a partial accumulator, and CUDA-core warps add the
-// partial to the running sum, kept in registers, with round-to-nearest FP32 adds.
+// four K steps (48 MMAs) from zero into a partial accumulator, and CUDA-core warps add the
+// partial to the running sum, kept in registers, with round-to-nearest FP32 adds (measured
+// error of the deep layers against the CPU convolution: below 4e-6 absolute).
 //
 // A persistent CTA (one per SM) walks 128-pixel x 128-channel (or x 64) output tiles.  GEMM
 // view: M = pixels of a TW x TH x NB tile, N = output channels, K = (32-channel chunk, filter
@@ -41,7 +42,8 @@
 //     accumulator drained);
 //   * warp 1 (converged, one elected lane issues): 12 tcgen05.mma per K step (4 K-slices x 3
 //     passes) into one of two partial accumulators in TMEM; after every second K step one
-//     tcgen05.commit hands the partial accumulator over and releases the operand stages;
+//     tcgen05.commit releases the operand stages, and every second of those also hands the
+//     partial accumulator over;
 //   * warps 12-19: read the partial accumulator (tcgen05.ld; a warp may touch the TMEM lanes
 //     of its quarter, two warps share a quarter and take half of the channels each), release
 //     it, add it to the running sum; after the tile's last K step store the sums, 256
@@ -69,7 +71,8 @@ constexpr int kTileBytes = BM * KC * 4;     // 16 KiB: one 128-row x 128-byte op
 constexpr int kPatchRows = 256;             // rows of 128 bytes an activation stage holds
 constexpr int kPatchBytes = kPatchRows * KC * 4;
 constexpr int kSmemTiles = kXStages * kPatchBytes + kWStages * 2 * kTileBytes;
-constexpr int kPromote = 2;                 // K steps accumulated on the tensor core before the FP32 add outside
+constexpr int kPromote = 2;                 // K steps per group: one commit, releases the operand stages
+constexpr int kSuper = 2;                   // groups accumulated on the tensor core before the FP32 add outside
 constexpr int kTmemCols = 512;              // 2 partial accumulators (<= 128 columns each) + 4 x 64 operand columns
 constexpr int kTmemA = 256;                 // first operand column
 constexpr int kGroups = 4;                  // "group done" barriers in rotation (a group = kPromote K steps)
@@ -212,6 +215,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
   const int taps = p.KS * p.KS;
   const int iters = taps * p.n_chunks;                      // K steps of a tile
   const int tile_groups = (iters + kPromote - 1) / kPromote;  // groups of a tile
+  const int tile_supers = (tile_groups + kSuper - 1) / kSuper;  // partial accumulators of a tile
   const int oc_tiles = (p.OC + BN - 1) / BN;
   const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_n * oc_tiles;
   auto decode = [&](int t, int &w0, int &h0, int &n0, int &oc0) {
@@ -272,11 +276,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     //      (with a single lane of a diverged warp every MMA pays for moving its operands there,
     //      and the issuing thread, not the tensor pipe, sets the pace). ----
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-    int g = 0, c = 0;  // K step and group of this CTA, counted across tiles
+    int g = 0, c = 0, sbase = 0;  // K step, group and first partial of the tile, counted across tiles
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, sbase += tile_supers) {
       for (int it0 = 0; it0 < iters && ok; it0 += kPromote, ++c) {
-        const int b = c & 1;
+        const int gi = it0 / kPromote;
+        const bool fresh = gi % kSuper == 0;            // the first MMA of a partial overwrites it
+        const int b = (sbase + gi / kSuper) & 1;
         // (the converters have also waited for the summing warps to drain this partial accumulator)
         const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
         const int it1 = min(it0 + kPromote, iters);
@@ -291,7 +297,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           if (elect_one()) {
 #pragma unroll
             for (int k = 0; k < KC / 8; ++k) {  // 32 bytes along K = 2 in the address field; w_lo follows w_hi
-              umma_tf32_ts(tmem_d, ta + k * 8, dlo + 2 * k, dhi, idesc, (it > it0 || k) ? 1u : 0u);
+              umma_tf32_ts(tmem_d, ta + k * 8, dlo + 2 * k, dhi, idesc, (!fresh || it > it0 || k) ? 1u : 0u);
               umma_tf32_ts(tmem_d, ta + KC + k * 8, dlo + 2 * k, dhi, idesc, 1u);
               umma_tf32_ts(tmem_d, ta + k * 8, dlo + 2 * k + (BN * KC * 4 >> 4), dhi, idesc, 1u);
             }
@@ -314,26 +320,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     const int pw = row % p.TW, ph = (row / p.TW) % p.TH, pn = row / (p.TW * p.TH);
     const int prow0 = pn < p.NB ? (pn * p.PH + ph) * p.PW + pw : 0;
     const bool live = pn < p.NB;
-    int g = 0, u = 0;
+    int g = 0, u = 0, sbase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, sbase += tile_supers) {
       for (int it = 0; it < iters; ++it, ++g) {
         const int chunk = it / taps, tap = it - chunk * taps;
         const int sx = u % kXStages, sa = g % kAStages;
         const bool last_of_chunk = tap == taps - 1;
         if ((g & 1) == set) {
-          // The MMA warp waits for afull only (a wait costs it ~150 clocks in which nothing is
-          // issued, and the tensor pipe holds only ~250 clocks of queued work), so afull stands
-          // for everything the MMAs of this K step need: the weights have landed and, at the
-          // first K step of a group, the summing warps have drained the partial accumulator
-          // the group adds into (two groups ago) ...
-          if (!(ok = mbar_wait_warp(bar_wfull(g % kWStages), (g / kWStages) & 1, abort_flag, lane))) break;
-          if (it % kPromote == 0) {
-            const int c = group_of(g);
-            if (!(ok = mbar_wait_warp(bar_pempty(c & 1), ((c >> 1) & 1) ^ 1, abort_flag, lane))) break;
-          }
-          // ... and the MMAs that read this operand stage four K steps ago have completed.
-          if (g >= kAStages && !(ok = wait_group_warp(group_of(g - kAStages)))) break;
+          // Read and split this tap's rows first: everything up to the tensor-memory store can
+          // be done while the operand stage is still in use.
           if (!(ok = mbar_wait_warp(bar_xfull(sx), (u / kXStages) & 1, abort_flag, lane))) break;
           const int r = tap / p.KS, q = tap - r * p.KS;
           const int prow = live ? prow0 + r * p.PW + q : 0;
@@ -350,6 +346,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
             hi[c] = round_tf32(v);
             lo[c] = round_tf32(v - __uint_as_float(hi[c]));
           }
+          // The MMA warp waits for afull only (a wait costs it ~150 clocks in which nothing is
+          // issued, and the tensor pipe holds only ~250 clocks of queued work), so afull stands
+          // for everything the MMAs of this K step need: the weights have landed and, at the
+          // first K step of a partial sum, the summing warps have drained the accumulator
+          // it goes into (two partial sums ago) ...
+          if (!(ok = mbar_wait_warp(bar_wfull(g % kWStages), (g / kWStages) & 1, abort_flag, lane))) break;
+          if (it % (kPromote * kSuper) == 0) {
+            const int sp = sbase + it / (kPromote * kSuper);
+            if (!(ok = mbar_wait_warp(bar_pempty(sp & 1), ((sp >> 1) & 1) ^ 1, abort_flag, lane))) break;
+          }
+          // ... and the MMAs that read this operand stage four K steps ago have completed.
+          if (g >= kAStages && !(ok = wait_group_warp(group_of(g - kAStages)))) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(kTmemA + sa * 2 * KC);
           tmem_st32(taddr, hi);
@@ -376,15 +384,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     const int row = quarter * 32 + lane;   // tile row = pixel = TMEM lane
     const int pw = row % p.TW, ph = (row / p.TW) % p.TH, pn = row / (p.TW * p.TH);
     const bool vec = (p.OC & 3) == 0;
-    int c = 0;
+    int cbase = 0, sp = 0;  // first group of the tile; partial sum, counted across tiles
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, cbase += tile_groups) {
       float acc[NC];
 #pragma unroll
       for (int j = 0; j < NC; ++j) acc[j] = 0.f;
-      for (int it0 = 0; it0 < iters; it0 += kPromote, ++c) {
-        const int b = c & 1;
-        if (!(ok = wait_group_warp(c))) break;
+      for (int si = 0; si < tile_supers; ++si, ++sp) {
+        const int b = sp & 1;
+        // the partial sum is complete when its last group is
+        if (!(ok = wait_group_warp(cbase + min((si + 1) * kSuper, tile_groups) - 1))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + half * NC);
 #pragma unroll
