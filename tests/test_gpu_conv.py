@@ -31,11 +31,11 @@ def device_conv(tb, torch, f, x_nchw, stride, pad, variant=0, poison=True):
 
 def covers(variant, ks, stride, ic=4):
     """The interpreter kernel is instantiated for 1x1 and 3x3, stride 1 and 2 only; the
-    tensor-core variant covers stride 1 with in_channel a multiple of 4."""
+    tensor-core variant needs in_channel to be a multiple of 4."""
     if variant == "interp":
         return ks in (1, 3) and stride in (1, 2)
     if variant == "tensor":
-        return stride == 1 and ic % 4 == 0
+        return ic % 4 == 0
     return True
 
 
@@ -182,6 +182,31 @@ def test_full_size_properties_vgg_layer(tb, torch_cuda, workloads):
     assert torch.allclose(lin, 2.0 * ya + run(b, 2), rtol=1e-4, atol=1e-4)
     one = run(a[3:4].contiguous(), 2, batch=1)   # odd batch takes the other pairing mode
     assert torch.allclose(one[0], ya[3], rtol=1e-5, atol=1e-6)
+
+
+def test_tensor_variant_long_accumulation(tb, torch_cuda, workloads, oracle):
+    """A 512-channel 3x3 layer adds ~1700 tensor-core results per output.  The tensor core
+    truncates when it adds into its accumulator; accumulated naively that drifts past the
+    tolerance, so this is the case that checks the chain is cut and summed outside."""
+    L = workloads.vgg19()[13]
+    filt = workloads.make_filter("vgg19", 13, L)
+    x = workloads.make_input("vgg19", 13, L, 2)
+    f = tb.SparseFilter(filt, L.IC, L.OC, L.KS)
+    got = device_conv(tb, torch_cuda, f, x, L.stride, L.pad, VARIANTS["tensor"])
+    check(oracle, got, oracle.host_conv2d(x, filt, L.stride, L.pad))
+
+
+def test_tensor_variant_stride2_full_width(tb, torch_cuda, workloads, oracle):
+    """Stride 2 takes the loader's box-per-K-step mode (element strides in the tensor map)."""
+    rng = np.random.default_rng(77)
+    ic, oc, h = 64, 96, 30
+    filt = rng.normal(0, 0.05, (oc, ic, 3, 3)).astype(np.float32)
+    filt[rng.random(filt.shape) < 0.8] = 0
+    x = rng.random((3, ic, h, h), dtype=np.float32)
+    f = tb.SparseFilter(filt, ic, oc, 3)
+    for stride, pad in ((2, 1), (2, 0), (3, 1)):
+        got = device_conv(tb, torch_cuda, f, x, stride, pad, VARIANTS["tensor"])
+        check(oracle, got, oracle.host_conv2d(x, filt, stride, pad))
 
 
 def test_timing_harness_runs(tb, torch_cuda):

@@ -51,7 +51,11 @@
 // Every barrier wait is bounded: on a timeout an error flag is raised, all roles drain, TMEM is
 // freed and the kernel returns; the host reports TETRIS_ERR_CUDA.
 //
-// No cluster launch, no multicast.  Covers stride 1, IC % 4 == 0 (TMA needs 16-byte strides).
+// At stride > 1 a patch would hold S*S times the pixels it is used for, so there the loader
+// falls back to one box per K step (the tile's input pixels of that tap, picked by the tensor
+// map's element strides) in a 4-deep ring of 16 KiB stages.
+//
+// No cluster launch, no multicast.  Covers strides 1-8, IC % 4 == 0 (TMA needs 16-byte strides).
 #include <cuda.h>
 
 #include <algorithm>
@@ -64,13 +68,14 @@ namespace tetris {
 namespace {
 
 constexpr int BM = 128, KC = 32;  // tile rows (pixels), K chunk (32 floats = 128 B); BN = 64 or 128 channels
-constexpr int kXStages = 2;                 // ring of activation tiles (shared memory, TMA target)
+constexpr int kXStages = 4;                 // activation stages: 4 of 16 KiB (a box per K step) or 2 of 32 KiB (patches)
 constexpr int kWStages = 5;                 // ring of {w_hi, w_lo} tile pairs (shared memory, TMA target)
 constexpr int kAStages = 4;                 // ring of {x, x_lo} operand blocks (tensor memory)
 constexpr int kTileBytes = BM * KC * 4;     // 16 KiB: one 128-row x 128-byte operand tile
 constexpr int kPatchRows = 256;             // rows of 128 bytes an activation stage holds
 constexpr int kPatchBytes = kPatchRows * KC * 4;
-constexpr int kSmemTiles = kXStages * kPatchBytes + kWStages * 2 * kTileBytes;
+constexpr int kXBytes = 2 * kPatchBytes;     // shared memory of the activation ring, either way
+constexpr int kSmemTiles = kXBytes + kWStages * 2 * kTileBytes;
 constexpr int kPromote = 2;                 // K steps per group: one commit, releases the operand stages
 constexpr int kSuper = 2;                   // groups accumulated on the tensor core before the FP32 add outside
 constexpr int kTmemCols = 512;              // 2 partial accumulators (<= 128 columns each) + 4 x 64 operand columns
@@ -85,6 +90,7 @@ struct TcParams {
   int N, OH, OW, OC, P, KS;
   int TW, TH, NB;              // pixels of a tile: TW x TH x NB <= 128 rows
   int PW, PH;                  // the tile with its halo: PW = TW + KS - 1, PH = TH + KS - 1
+  int per_tap, S;              // per_tap: one strided box per K step instead of a patch per chunk (stride > 1)
   int tiles_w, tiles_h, tiles_n;
   int n_chunks;                // ceil(IC / 32)
   int *error_flag;
@@ -180,7 +186,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char *xbase = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
-  unsigned char *wbase = xbase + kXStages * kPatchBytes;
+  unsigned char *wbase = xbase + kXBytes;
   uint64_t *bars = reinterpret_cast<uint64_t *>(xbase + kSmemTiles);
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -193,7 +199,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
   auto bar_pempty = [&](int b) { return smem_u32(&bars[kNumBars - 2 + b]); };
 
   if (tid == 0) {
-    for (int s = 0; s < kXStages; ++s) { mbar_init(bar_xfull(s), 1); mbar_init(bar_xempty(s), 8); }
+    // a patch is read by all eight converter warps, a per-tap box by the four that take its K step
+    for (int s = 0; s < kXStages; ++s) { mbar_init(bar_xfull(s), 1); mbar_init(bar_xempty(s), p.per_tap ? 4 : 8); }
     for (int s = 0; s < kWStages; ++s) mbar_init(bar_wfull(s), 1);
     for (int s = 0; s < kAStages; ++s) mbar_init(bar_afull(s), 4);
     for (int c = 0; c < kGroups; ++c) mbar_init(bar_gdone(c), 1);
@@ -237,18 +244,36 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
   if (warp == 0) {
     // ---- activation loads ----
     if (lane == 0) {
-      // One patch per 32-channel chunk: the tile plus its halo, shared by all taps.
-      const uint32_t x_box_bytes = (uint32_t)(p.PW * p.PH * p.NB * KC * 4);
-      int u = 0;  // patch count of this CTA, across tiles
+      int u = 0;  // loads of this CTA, across tiles
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        int w0, h0, n0, oc0;
-        decode(t, w0, h0, n0, oc0);
-        for (int chunk = 0; chunk < p.n_chunks; ++chunk, ++u) {
-          const int s = u % kXStages;
-          if (!(ok = mbar_wait(bar_xempty(s), ((u / kXStages) & 1) ^ 1, abort_flag))) break;
-          mbar_expect_tx(bar_xfull(s), x_box_bytes);
-          tma_load_4d(smem_u32(xbase + s * kPatchBytes), &map_x, bar_xfull(s), chunk * KC, w0 - p.P, h0 - p.P, n0);
+      if (!p.per_tap) {
+        // One patch per 32-channel chunk: the tile plus its halo, shared by all taps.
+        const uint32_t x_box_bytes = (uint32_t)(p.PW * p.PH * p.NB * KC * 4);
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+          int w0, h0, n0, oc0;
+          decode(t, w0, h0, n0, oc0);
+          for (int chunk = 0; chunk < p.n_chunks; ++chunk, ++u) {
+            const int s = u & 1;
+            if (!(ok = mbar_wait(bar_xempty(s), ((u >> 1) & 1) ^ 1, abort_flag))) break;
+            mbar_expect_tx(bar_xfull(s), x_box_bytes);
+            tma_load_4d(smem_u32(xbase + s * kPatchBytes), &map_x, bar_xfull(s), chunk * KC, w0 - p.P, h0 - p.P, n0);
+          }
+        }
+      } else {
+        // Stride > 1: one box per K step, the tile's input pixels of that tap (every S-th
+        // pixel; the tensor map carries the element strides).
+        const uint32_t x_box_bytes = (uint32_t)(p.TW * p.TH * p.NB * KC * 4);
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+          int w0, h0, n0, oc0;
+          decode(t, w0, h0, n0, oc0);
+          for (int it = 0; it < iters; ++it, ++u) {
+            const int s = u % kXStages;
+            if (!(ok = mbar_wait(bar_xempty(s), ((u / kXStages) & 1) ^ 1, abort_flag))) break;
+            const int chunk = it / taps, tap = it - chunk * taps;
+            const int r = tap / p.KS, q = tap - r * p.KS;
+            mbar_expect_tx(bar_xfull(s), x_box_bytes);
+            tma_load_4d(smem_u32(xbase + s * kTileBytes), &map_x, bar_xfull(s), chunk * KC, w0 * p.S + q - p.P, h0 * p.S + r - p.P, n0);
+          }
         }
       }
     }
@@ -325,15 +350,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, sbase += tile_supers) {
       for (int it = 0; it < iters; ++it, ++g) {
         const int chunk = it / taps, tap = it - chunk * taps;
-        const int sx = u % kXStages, sa = g % kAStages;
+        const int sa = g % kAStages;
+        // activation stage, its phase, and whether this K step is the last to read it
+        const int sx = p.per_tap ? g % kXStages : u & 1;
+        const uint32_t xphase = (uint32_t)(p.per_tap ? g / kXStages : u >> 1) & 1u;
         const bool last_of_chunk = tap == taps - 1;
         if ((g & 1) == set) {
           // Read and split this tap's rows first: everything up to the tensor-memory store can
           // be done while the operand stage is still in use.
-          if (!(ok = mbar_wait_warp(bar_xfull(sx), (u / kXStages) & 1, abort_flag, lane))) break;
+          if (!(ok = mbar_wait_warp(bar_xfull(sx), xphase, abort_flag, lane))) break;
           const int r = tap / p.KS, q = tap - r * p.KS;
-          const int prow = live ? prow0 + r * p.PW + q : 0;
-          const unsigned char *src = xbase + sx * kPatchBytes + prow * 128;
+          const int prow = p.per_tap ? row : live ? prow0 + r * p.PW + q : 0;
+          const unsigned char *src = xbase + (p.per_tap ? sx * kTileBytes : sx * kPatchBytes) + prow * 128;
           uint32_t hi[32], lo[32];
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
@@ -365,14 +393,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_afull(sa));
+          if (lane == 0) {
+            mbar_arrive(bar_afull(sa));
+            if (p.per_tap) mbar_arrive(bar_xempty(sx));  // a per-tap box has this one reader set
+          }
         }
         // The patch is released by every warp once its own last K step of the chunk is behind
         // the tensor-memory store.  (Releasing a stage right after the loads, ahead of long
         // waits, produced wrong results on the 56x56 and 112x112 layers.)
         if (last_of_chunk) {
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_xempty(sx));
+          if (lane == 0 && !p.per_tap) mbar_arrive(bar_xempty(sx));
           ++u;
         }
       }
@@ -472,10 +503,9 @@ EncodeFn get_encode() {
 }
 
 int encode_map(CUtensorMap *map, void *ptr, int rank, const cuuint64_t *dims, const cuuint64_t *strides,
-               const cuuint32_t *box) {
+               const cuuint32_t *box, const cuuint32_t *estr) {
   EncodeFn enc = get_encode();
   if (!enc) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return TETRIS_ERR_UNSUPPORTED; }
-  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, ptr, dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -535,13 +565,13 @@ int conv_tc_prepare(tetris_filter *f, const float *d_dense) {
 
 bool conv_tc_supported(const tetris_filter *f, const ConvShape &s) {
   if (!f->tc_state || f->groups != 1) return false;
-  if (s.S != 1 || (s.IC & 3) != 0 || s.N < 1 || s.OH < 1 || s.OW < 1) return false;
+  if (s.S < 1 || s.S > 8 || (s.IC & 3) != 0 || s.N < 1 || s.OH < 1 || s.OW < 1) return false;
   return true;
 }
 
 int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const ConvShape &s, cudaStream_t st) {
   if (!conv_tc_supported(f, s) || (reinterpret_cast<uintptr_t>(in) & 15) != 0) {
-    set_error("tensor-core variant covers stride 1, in_channel %% 4 == 0 and 16-byte aligned inputs only");
+    set_error("tensor-core variant covers strides up to 8, in_channel %% 4 == 0 and 16-byte aligned inputs only");
     return TETRIS_ERR_UNSUPPORTED;
   }
   TcState *t = static_cast<TcState *>(f->tc_state);
@@ -554,34 +584,39 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
     const ConvShape &l = t->last_shape;
     const bool hit = t->last_in == in && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S;
     if (!hit) {
-      // pixels of a tile: TW x TH x NB rows, at most 128, as full as possible, and such that
-      // the tile with its halo fits an activation stage
+      // pixels of a tile: TW x TH x NB rows, at most 128, as full as possible, and -- at stride
+      // 1, where all taps read one patch -- such that the tile with its halo fits a stage
+      const bool per_tap = s.S > 1;
+      const int halo = per_tap ? 0 : s.KS - 1;
       int best_tw = 0, best_th = 1, best_nb = 1;
       double best = -1.0;
       for (int TW = 1; TW <= std::min(s.OW, 128); ++TW) {
         int TH = std::min(s.OH, 128 / TW);
-        while (TH > 1 && (TW + s.KS - 1) * (TH + s.KS - 1) > kPatchRows) --TH;
-        if (TH < 1 || (TW + s.KS - 1) * (TH + s.KS - 1) > kPatchRows) continue;
+        while (TH > 1 && (TW + halo) * (TH + halo) > kPatchRows) --TH;
+        if (TH < 1 || (TW + halo) * (TH + halo) > kPatchRows || TW * s.S > 256 || TH * s.S > 256) continue;
         int NB = (TH == s.OH && TW == s.OW) ? std::min(s.N, 128 / (TW * TH)) : 1;
-        while (NB > 1 && (TW + s.KS - 1) * (TH + s.KS - 1) * NB > kPatchRows) --NB;
+        while (NB > 1 && (TW + halo) * (TH + halo) * NB > kPatchRows) --NB;
         const double tiles = (double)((s.OW + TW - 1) / TW) * ((s.OH + TH - 1) / TH) * ((s.N + NB - 1) / NB);
         const double eff = (double)s.N * s.OH * s.OW / (tiles * 128.0);
         if (eff > best) { best = eff; best_tw = TW; best_th = TH; best_nb = NB; }
       }
       if (best_tw == 0) {
-        set_error("tensor-core variant: no tile of this layer fits an activation stage with its halo");
+        set_error("tensor-core variant: no tile of this layer fits an activation stage");
         return TETRIS_ERR_UNSUPPORTED;
       }
-      const int PW = best_tw + s.KS - 1, PH = best_th + s.KS - 1;
+      const int PW = best_tw + halo, PH = best_th + halo;
       const cuuint64_t dims[4] = {(cuuint64_t)s.IC, (cuuint64_t)s.W, (cuuint64_t)s.H, (cuuint64_t)s.N};
       const cuuint64_t strides[3] = {(cuuint64_t)s.IC * 4, (cuuint64_t)s.IC * 4 * s.W, (cuuint64_t)s.IC * 4 * s.W * s.H};
-      const cuuint32_t box[4] = {KC, (cuuint32_t)PW, (cuuint32_t)PH, (cuuint32_t)best_nb};
-      const int rc = encode_map(&t->map_x, const_cast<float *>(in), 4, dims, strides, box);
+      // with element strides the box spans S times the pixels it loads
+      const cuuint32_t box[4] = {KC, (cuuint32_t)(PW * s.S), (cuuint32_t)(PH * s.S), (cuuint32_t)best_nb};
+      const cuuint32_t estr[4] = {1, (cuuint32_t)s.S, (cuuint32_t)s.S, 1};
+      const int rc = encode_map(&t->map_x, const_cast<float *>(in), 4, dims, strides, box, estr);
       if (rc) return rc;
       TcParams &q = t->params;
       q.N = s.N; q.OH = s.OH; q.OW = s.OW; q.OC = s.OC; q.P = s.P; q.KS = s.KS;
       q.TW = best_tw; q.TH = best_th; q.NB = best_nb;
       q.PW = PW; q.PH = PH;
+      q.per_tap = per_tap ? 1 : 0; q.S = s.S;
       q.tiles_w = (s.OW + best_tw - 1) / best_tw;
       q.tiles_h = (s.OH + best_th - 1) / best_th;
       q.tiles_n = (s.N + best_nb - 1) / best_nb;

@@ -429,7 +429,7 @@ void fill_plan(const tetris_filter *f, const ConvShape &s, const Candidate &c, i
 double tc_cost(const tetris_filter *f, const ConvShape &s, int sm_count) {
   const double tiles = std::ceil((double)s.N * s.OH * s.OW / 128.0 / 0.9) * ((s.OC + 127) / 128);
   const double iters = (double)s.KS * s.KS * ((s.IC + 31) / 32);
-  return std::ceil(tiles / sm_count) * (iters * 1700.0 + 8000.0);
+  return std::ceil(tiles / sm_count) * (iters * 1500.0 + 8000.0);  // measured clocks per K step and per tile
 }
 
 int make_plan(const tetris_filter *f, const ConvShape &s, Plan *plan) {
