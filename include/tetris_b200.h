@@ -56,7 +56,7 @@ enum {
   TETRIS_VARIANT_INTERP = 3,  /* shared-memory tile, jump-table interpreter that reuses a
                                  register-resident input window across channels (1x1, 3x3) */
   TETRIS_VARIANT_TENSOR = 4   /* dense contraction on the tensor cores (tcgen05, split TF32);
-                                 stride 1, in_channel % 4 == 0                            */
+                                 strides 1-8, in_channel % 4 == 0, 16-byte aligned input  */
 };
 
 typedef struct tetris_filter tetris_filter_t; /* opaque; owns device buffers */
