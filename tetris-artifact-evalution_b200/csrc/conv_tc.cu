@@ -93,6 +93,7 @@ struct TcParams {
   int per_tap, S;              // per_tap: one strided box per K step instead of a patch per chunk (stride > 1)
   int tiles_w, tiles_h, tiles_n;
   int n_chunks;                // ceil(IC / 32)
+  int ksplit;                  // work items per tile: each takes n_chunks / ksplit chunks and adds its result in
   int *error_flag;
   const float *w_tiles;        // weight tile images, see tc_weight_tiles_kernel
 };
@@ -220,12 +221,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
   // Persistent CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the channel tile is the
   // fastest index, so CTAs that run side by side read the same activation patch.
   const int taps = p.KS * p.KS;
-  const int iters = taps * p.n_chunks;                      // K steps of a tile
+  const int item_chunks = p.n_chunks / p.ksplit;            // chunks of a work item (ksplit divides n_chunks)
+  const int iters = taps * item_chunks;                     // K steps of a work item
   const int tile_groups = (iters + kPromote - 1) / kPromote;  // groups of a tile
   const int tile_supers = (tile_groups + kSuper - 1) / kSuper;  // partial accumulators of a tile
   const int oc_tiles = (p.OC + BN - 1) / BN;
-  const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_n * oc_tiles;
-  auto decode = [&](int t, int &w0, int &h0, int &n0, int &oc0) {
+  // A work item is a tile, or -- when the tiles do not fill the last wave of CTAs well -- one
+  // of ksplit slices of a tile's K range; the slices add their results into a zeroed output.
+  const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_n * oc_tiles * p.ksplit;
+  auto decode = [&](int t, int &w0, int &h0, int &n0, int &oc0, int &chunk0) {
+    chunk0 = (t % p.ksplit) * item_chunks; t /= p.ksplit;
     oc0 = (t % oc_tiles) * BN; t /= oc_tiles;
     w0 = (t % p.tiles_w) * p.TW; t /= p.tiles_w;
     h0 = (t % p.tiles_h) * p.TH;
@@ -250,9 +255,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         // One patch per 32-channel chunk: the tile plus its halo, shared by all taps.
         const uint32_t x_box_bytes = (uint32_t)(p.PW * p.PH * p.NB * KC * 4);
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-          int w0, h0, n0, oc0;
-          decode(t, w0, h0, n0, oc0);
-          for (int chunk = 0; chunk < p.n_chunks; ++chunk, ++u) {
+          int w0, h0, n0, oc0, chunk0;
+          decode(t, w0, h0, n0, oc0, chunk0);
+          for (int chunk = chunk0; chunk < chunk0 + item_chunks; ++chunk, ++u) {
             const int s = u & 1;
             if (!(ok = mbar_wait(bar_xempty(s), ((u >> 1) & 1) ^ 1, abort_flag))) break;
             mbar_expect_tx(bar_xfull(s), x_box_bytes);
@@ -264,15 +269,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         // pixel; the tensor map carries the element strides).
         const uint32_t x_box_bytes = (uint32_t)(p.TW * p.TH * p.NB * KC * 4);
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-          int w0, h0, n0, oc0;
-          decode(t, w0, h0, n0, oc0);
+          int w0, h0, n0, oc0, chunk0;
+          decode(t, w0, h0, n0, oc0, chunk0);
           for (int it = 0; it < iters; ++it, ++u) {
             const int s = u % kXStages;
             if (!(ok = mbar_wait(bar_xempty(s), ((u / kXStages) & 1) ^ 1, abort_flag))) break;
             const int chunk = it / taps, tap = it - chunk * taps;
             const int r = tap / p.KS, q = tap - r * p.KS;
             mbar_expect_tx(bar_xfull(s), x_box_bytes);
-            tma_load_4d(smem_u32(xbase + s * kTileBytes), &map_x, bar_xfull(s), chunk * KC, w0 * p.S + q - p.P, h0 * p.S + r - p.P, n0);
+            tma_load_4d(smem_u32(xbase + s * kTileBytes), &map_x, bar_xfull(s), (chunk0 + chunk) * KC, w0 * p.S + q - p.P, h0 * p.S + r - p.P, n0);
           }
         }
       }
@@ -283,13 +288,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
       int g = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        int w0, h0, n0, oc0;
-        decode(t, w0, h0, n0, oc0);
+        int w0, h0, n0, oc0, chunk0;
+        decode(t, w0, h0, n0, oc0, chunk0);
         for (int it = 0; it < iters; ++it, ++g) {
           const int s = g % kWStages;
           if (g >= kWStages && !(ok = wait_group(group_of(g - kWStages)))) break;
           // K step `it` of channel tile oc0 / BN: one contiguous {w_hi, w_lo} image
-          const float *src = p.w_tiles + ((size_t)it * oc_tiles + oc0 / BN) * (2 * BN * KC);
+          const float *src = p.w_tiles + ((size_t)(chunk0 * taps + it) * oc_tiles + oc0 / BN) * (2 * BN * KC);
           mbar_expect_tx(bar_wfull(s), (uint32_t)(2 * BN * KC * 4));
           bulk_load(smem_u32(wbase + s * 2 * kTileBytes), src, (uint32_t)(2 * BN * KC * 4), bar_wfull(s));
         }
@@ -441,13 +446,23 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         }
       }
       if (!ok) break;
-      int w0, h0, n0, oc0;
-      decode(t, w0, h0, n0, oc0);
+      int w0, h0, n0, oc0, chunk0;
+      decode(t, w0, h0, n0, oc0, chunk0);
       const int ow = w0 + pw, oh = h0 + ph, n = n0 + pn;
       if (!(pn < p.NB && ow < p.OW && oh < p.OH && n < p.N) || *abort_flag) continue;
       const int ocb = oc0 + half * NC;
       float *o = p.out + (((size_t)n * p.OH + oh) * p.OW + ow) * p.OC + ocb;
-      if (vec && ocb + NC <= p.OC) {
+      if (p.ksplit > 1) {  // a slice of the K range: add into the zeroed output
+        if (vec && ocb + NC <= p.OC) {
+#pragma unroll
+          for (int j = 0; j < NC; j += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + j), "f"(acc[j]), "f"(acc[j + 1]), "f"(acc[j + 2]), "f"(acc[j + 3]) : "memory");
+        } else {
+#pragma unroll
+          for (int j = 0; j < NC; ++j)
+            if (ocb + j < p.OC) atomicAdd(o + j, acc[j]);
+        }
+      } else if (vec && ocb + NC <= p.OC) {
 #pragma unroll
         for (int j = 0; j < NC; j += 4) *reinterpret_cast<float4 *>(o + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
       } else {
@@ -626,7 +641,23 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
       int dev = 0, sms = 0;
       TETRIS_CUDA_TRY(cudaGetDevice(&dev));
       TETRIS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-      const long long total = (long long)q.tiles_w * q.tiles_h * q.tiles_n * ((s.OC + t->bn - 1) / t->bn);
+      const long long tiles = (long long)q.tiles_w * q.tiles_h * q.tiles_n * ((s.OC + t->bn - 1) / t->bn);
+      // Split the K range of every tile into d work items when that fills the waves of CTAs
+      // better (e.g. 448 tiles on 148 SMs: 4 waves for 3.03 waves of work).  Cost in K steps:
+      // waves x (K steps + ~10 for filling and draining the pipeline per item), plus zeroing
+      // the output that the items add into.  Measured on 28x28x512 -> 512: 0.396 ms unsplit,
+      // 0.357 ms in two slices, 0.349 ms in four.
+      const double iters = (double)s.KS * s.KS * q.n_chunks;
+      const double zeroing = ((double)s.N * s.OH * s.OW * s.OC * 4 / 6.0e12 + 3e-6) * 1.9e9 / 1450.0;
+      int best_d = 1;
+      double best_cost = std::ceil((double)tiles / sms) * (iters + 10.0);
+      for (int d = 2; d <= 8 && d <= q.n_chunks; ++d) {
+        if (q.n_chunks % d) continue;
+        const double cost = std::ceil((double)tiles * d / sms) * (iters / d + 10.0) + zeroing;
+        if (cost < 0.96 * best_cost) { best_cost = cost; best_d = d; }
+      }
+      q.ksplit = best_d;
+      const long long total = tiles * best_d;
       t->grid = dim3((unsigned)std::min<long long>(total, sms));  // persistent: one CTA per SM
       t->last_in = in;
       t->last_shape = s;
@@ -646,6 +677,8 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
     TETRIS_CUDA_TRY(cudaFuncSetAttribute(conv_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (dev < 16) configured[dev] = true;
   }
+  if (p.ksplit > 1)  // the work items add into the output
+    TETRIS_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)s.N * s.OH * s.OW * s.OC * sizeof(float), st));
   if (bn == 64)
     conv_tc_kernel<64><<<grid, kThreads, smem, st>>>(map_x, p);
   else
