@@ -55,7 +55,8 @@
 // falls back to one box per K step (the tile's input pixels of that tap, picked by the tensor
 // map's element strides) in a 4-deep ring of 16 KiB stages.
 //
-// No cluster launch, no multicast.  Covers strides 1-8, IC % 4 == 0 (TMA needs 16-byte strides).
+// No cluster launch: every load is issued by one CTA for itself.  Covers strides 1-8, IC % 4 == 0
+// (TMA needs 16-byte strides).
 #include <cuda.h>
 
 #include <algorithm>
@@ -307,6 +308,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     //      and the issuing thread, not the tensor pipe, sets the pace). ----
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     int g = 0, c = 0, sbase = 0;  // K step, group and first partial of the tile, counted across tiles
+    int sw = 0;                   // weight stage of K step g
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, sbase += tile_supers) {
       for (int it0 = 0; it0 < iters && ok; it0 += kPromote, ++c) {
@@ -317,7 +319,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
         const int it1 = min(it0 + kPromote, iters);
         for (int it = it0; it < it1; ++it, ++g) {
-          const int sw = g % kWStages, sa = g % kAStages;
+          const int sa = g % kAStages;  // a power of two; the weight stage `sw` is counted
           // one wait per K step: afull stands for all inputs of the step (see the converters)
           if (!(ok = mbar_wait_warp(bar_afull(sa), (g / kAStages) & 1, abort_flag, lane))) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -333,6 +335,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
             }
           }
           __syncwarp();
+          if (++sw == kWStages) sw = 0;
         }
         if (ok && elect_one()) umma_commit(bar_gdone(c % kGroups));  // arrives when the group's last MMA has completed
         __syncwarp();
@@ -350,11 +353,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     const int pw = row % p.TW, ph = (row / p.TW) % p.TH, pn = row / (p.TW * p.TH);
     const int prow0 = pn < p.NB ? (pn * p.PH + ph) * p.PW + pw : 0;
     const bool live = pn < p.NB;
-    int g = 0, u = 0, sbase = 0;
+    // Everything that depends on the K step is counted along (no divisions in this loop: the
+    // converters' own instruction count is on the critical path).
+    int g = 0, u = 0, sbase = 0, cbase = 0;  // K step, patch, first partial / first group of the tile
+    int ws = 0;                              // weight stage of K step g and its phase
+    uint32_t wphase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, sbase += tile_supers) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, sbase += tile_supers, cbase += tile_groups) {
+      int tap = 0, r = 0, q = 0;
       for (int it = 0; it < iters; ++it, ++g) {
-        const int chunk = it / taps, tap = it - chunk * taps;
         const int sa = g % kAStages;
         // activation stage, its phase, and whether this K step is the last to read it
         const int sx = p.per_tap ? g % kXStages : u & 1;
@@ -364,7 +371,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           // Read and split this tap's rows first: everything up to the tensor-memory store can
           // be done while the operand stage is still in use.
           if (!(ok = mbar_wait_warp(bar_xfull(sx), xphase, abort_flag, lane))) break;
-          const int r = tap / p.KS, q = tap - r * p.KS;
           const int prow = p.per_tap ? row : live ? prow0 + r * p.PW + q : 0;
           const unsigned char *src = xbase + (p.per_tap ? sx * kTileBytes : sx * kPatchBytes) + prow * 128;
           uint32_t hi[32], lo[32];
@@ -384,13 +390,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           // for everything the MMAs of this K step need: the weights have landed and, at the
           // first K step of a partial sum, the summing warps have drained the accumulator
           // it goes into (two partial sums ago) ...
-          if (!(ok = mbar_wait_warp(bar_wfull(g % kWStages), (g / kWStages) & 1, abort_flag, lane))) break;
+          if (!(ok = mbar_wait_warp(bar_wfull(ws), wphase, abort_flag, lane))) break;
           if (it % (kPromote * kSuper) == 0) {
             const int sp = sbase + it / (kPromote * kSuper);
             if (!(ok = mbar_wait_warp(bar_pempty(sp & 1), ((sp >> 1) & 1) ^ 1, abort_flag, lane))) break;
           }
           // ... and the MMAs that read this operand stage four K steps ago have completed.
-          if (g >= kAStages && !(ok = wait_group_warp(group_of(g - kAStages)))) break;
+          // (group of K step g - 4: two groups back in this tile, or near the end of the last)
+          if (g >= kAStages) {
+            const int cprev = it >= kAStages      ? cbase + (it - kAStages) / kPromote
+                              : iters >= kAStages ? cbase - tile_groups + (iters + it - kAStages) / kPromote
+                                                  : group_of(g - kAStages);  // tiles of fewer than 4 K steps
+            if (!(ok = wait_group_warp(cprev))) break;
+          }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(kTmemA + sa * 2 * KC);
           tmem_st32(taddr, hi);
@@ -410,7 +422,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           __syncwarp();
           if (lane == 0 && !p.per_tap) mbar_arrive(bar_xempty(sx));
           ++u;
+          tap = 0; r = 0; q = 0;
+        } else {
+          ++tap;
+          if (++q == p.KS) { q = 0; ++r; }
         }
+        if (++ws == kWStages) { ws = 0; wphase ^= 1u; }
       }
     }
   } else if (warp >= 12) {
