@@ -83,7 +83,7 @@ constexpr int kTmemCols = 512;              // 2 partial accumulators (<= 128 co
 constexpr int kTmemA = 256;                 // first operand column
 constexpr int kGroups = 4;                  // "group done" barriers in rotation (a group = kPromote K steps)
 constexpr int kThreads = 640;               // warp 0 x loads, 1 MMA, 2 w loads, 4-11 convert, 12-19 sum + store
-constexpr int kNumBars = 2 * kXStages + kWStages + kAStages + kGroups + 2;
+constexpr int kNumBars = 2 * kXStages + kWStages + 2 * kAStages + kGroups + 2;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct TcParams {
@@ -197,14 +197,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
   auto bar_xempty = [&](int s) { return smem_u32(&bars[kXStages + s]); };
   auto bar_wfull = [&](int s) { return smem_u32(&bars[2 * kXStages + s]); };
   auto bar_afull = [&](int s) { return smem_u32(&bars[2 * kXStages + kWStages + s]); };
-  auto bar_gdone = [&](int c) { return smem_u32(&bars[2 * kXStages + kWStages + kAStages + c]); };
+  auto bar_ready = [&](int s) { return smem_u32(&bars[2 * kXStages + kWStages + kAStages + s]); };
+  auto bar_gdone = [&](int c) { return smem_u32(&bars[2 * kXStages + kWStages + 2 * kAStages + c]); };
   auto bar_pempty = [&](int b) { return smem_u32(&bars[kNumBars - 2 + b]); };
 
   if (tid == 0) {
     // a patch is read by all eight converter warps, a per-tap box by the four that take its K step
     for (int s = 0; s < kXStages; ++s) { mbar_init(bar_xfull(s), 1); mbar_init(bar_xempty(s), p.per_tap ? 4 : 8); }
     for (int s = 0; s < kWStages; ++s) mbar_init(bar_wfull(s), 1);
-    for (int s = 0; s < kAStages; ++s) mbar_init(bar_afull(s), 4);
+    for (int s = 0; s < kAStages; ++s) { mbar_init(bar_afull(s), 4); mbar_init(bar_ready(s), 1); }
     for (int c = 0; c < kGroups; ++c) mbar_init(bar_gdone(c), 1);
     for (int b = 0; b < 2; ++b) mbar_init(bar_pempty(b), 8);
     *abort_flag = 0;
@@ -341,6 +342,36 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         __syncwarp();
       }
     }
+  } else if (warp == 3) {
+    // ---- gatekeeper (one thread): collects, per K step, the conditions under which the
+    //      converters may store the step's operand and the MMAs may run -- the weights have
+    //      landed; at the first K step of a partial sum the summing warps have drained the
+    //      accumulator it goes into (two partial sums ago); the MMAs that read the operand stage
+    //      four K steps ago have completed -- and passes them on as ONE barrier.  A wait costs
+    //      a converter warp 150-300 clocks even on a completed phase, and the converters'
+    //      per-step latency is what limits the kernel.
+    if (lane == 0) {
+      int g = 0, sbase = 0, cbase = 0, ws = 0;
+      uint32_t wphase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, sbase += tile_supers, cbase += tile_groups) {
+        for (int it = 0; it < iters; ++it, ++g) {
+          if (!(ok = mbar_wait(bar_wfull(ws), wphase, abort_flag))) break;
+          if (it % (kPromote * kSuper) == 0) {
+            const int sp = sbase + it / (kPromote * kSuper);
+            if (!(ok = mbar_wait(bar_pempty(sp & 1), ((sp >> 1) & 1) ^ 1, abort_flag))) break;
+          }
+          if (g >= kAStages) {  // group of K step g - 4: two groups back in this tile, or near the end of the last
+            const int cprev = it >= kAStages      ? cbase + (it - kAStages) / kPromote
+                              : iters >= kAStages ? cbase - tile_groups + (iters + it - kAStages) / kPromote
+                                                  : group_of(g - kAStages);  // tiles of fewer than 4 K steps
+            if (!(ok = wait_group(cprev))) break;
+          }
+          mbar_arrive(bar_ready(g % kAStages));
+          if (++ws == kWStages) { ws = 0; wphase ^= 1u; }
+        }
+      }
+    }
   } else if (warp >= 4 && warp < 12) {
     // ---- warps 4..11: shared activation tile -> {x_hi, x_lo} in tensor memory.  A warp may
     //      touch only the TMEM lanes of its quarter (warp % 4); two warps share a quarter and
@@ -355,11 +386,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     const bool live = pn < p.NB;
     // Everything that depends on the K step is counted along (no divisions in this loop: the
     // converters' own instruction count is on the critical path).
-    int g = 0, u = 0, sbase = 0, cbase = 0;  // K step, patch, first partial / first group of the tile
-    int ws = 0;                              // weight stage of K step g and its phase
-    uint32_t wphase = 0;
+    int g = 0, u = 0;                        // K step and patch of this CTA, counted across tiles
+    int seen_u = -1;                         // patch this warp has already waited for
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, sbase += tile_supers, cbase += tile_groups) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int tap = 0, r = 0, q = 0;
       for (int it = 0; it < iters; ++it, ++g) {
         const int sa = g % kAStages;
@@ -370,7 +400,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         if ((g & 1) == set) {
           // Read and split this tap's rows first: everything up to the tensor-memory store can
           // be done while the operand stage is still in use.
-          if (!(ok = mbar_wait_warp(bar_xfull(sx), xphase, abort_flag, lane))) break;
+          if (p.per_tap || seen_u != u) {  // a patch is waited for once, at the first tap this warp reads
+            if (!(ok = mbar_wait_warp(bar_xfull(sx), xphase, abort_flag, lane))) break;
+            seen_u = u;
+          }
           const int prow = p.per_tap ? row : live ? prow0 + r * p.PW + q : 0;
           const unsigned char *src = xbase + (p.per_tap ? sx * kTileBytes : sx * kPatchBytes) + prow * 128;
           uint32_t hi[32], lo[32];
@@ -387,22 +420,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           }
           // The MMA warp waits for afull only (a wait costs it ~150 clocks in which nothing is
           // issued, and the tensor pipe holds only ~250 clocks of queued work), so afull stands
-          // for everything the MMAs of this K step need: the weights have landed and, at the
-          // first K step of a partial sum, the summing warps have drained the accumulator
-          // it goes into (two partial sums ago) ...
-          if (!(ok = mbar_wait_warp(bar_wfull(ws), wphase, abort_flag, lane))) break;
-          if (it % (kPromote * kSuper) == 0) {
-            const int sp = sbase + it / (kPromote * kSuper);
-            if (!(ok = mbar_wait_warp(bar_pempty(sp & 1), ((sp >> 1) & 1) ^ 1, abort_flag, lane))) break;
-          }
-          // ... and the MMAs that read this operand stage four K steps ago have completed.
-          // (group of K step g - 4: two groups back in this tile, or near the end of the last)
-          if (g >= kAStages) {
-            const int cprev = it >= kAStages      ? cbase + (it - kAStages) / kPromote
-                              : iters >= kAStages ? cbase - tile_groups + (iters + it - kAStages) / kPromote
-                                                  : group_of(g - kAStages);  // tiles of fewer than 4 K steps
-            if (!(ok = wait_group_warp(cprev))) break;
-          }
+          // for everything the MMAs of this K step need; the gatekeeper has collected the rest.
+          if (!(ok = mbar_wait_warp(bar_ready(sa), (g / kAStages) & 1, abort_flag, lane))) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(kTmemA + sa * 2 * KC);
           tmem_st32(taddr, hi);
@@ -427,7 +446,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           ++tap;
           if (++q == p.KS) { q = 0; ++r; }
         }
-        if (++ws == kWStages) { ws = 0; wphase ^= 1u; }
       }
     }
   } else if (warp >= 12) {
