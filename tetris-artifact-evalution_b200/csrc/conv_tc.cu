@@ -38,8 +38,11 @@
 //     a 5-deep ring;
 //   * warps 4-11: per K step read the patch rows of the tap (un-swizzling) and write
 //     x_hi = tf32(x) and x_lo = tf32(x - x_hi) into a 4-deep ring of 64 TMEM columns
-//     (tcgen05.st); they also do the waiting for the MMA warp (weights landed, partial
-//     accumulator drained);
+//     (tcgen05.st); warps 4-7 take the even K steps, warps 8-11 the odd ones, because one
+//     step's chain of waits, loads and stores is longer than an MMA period;
+//   * warp 3 (one thread), the gatekeeper: waits per K step for the weights, for the drained
+//     partial accumulator and for the free operand stage, and passes all three on as one
+//     barrier, so that a converter warp waits once per K step and the MMA warp once;
 //   * warp 1 (converged, one elected lane issues): 12 tcgen05.mma per K step (4 K-slices x 3
 //     passes) into one of two partial accumulators in TMEM; after every second K step one
 //     tcgen05.commit releases the operand stages, and every second of those also hands the
@@ -636,7 +639,8 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
     if (!hit) {
       // pixels of a tile: TW x TH x NB rows, at most 128, as full as possible, and -- at stride
       // 1, where all taps read one patch -- such that the tile with its halo fits a stage
-      const bool per_tap = s.S > 1;
+      // (1x1 filters have no halo to share either, and the per-K-step ring is four deep)
+      const bool per_tap = s.S > 1 || s.KS == 1;
       const int halo = per_tap ? 0 : s.KS - 1;
       int best_tw = 0, best_th = 1, best_nb = 1;
       double best = -1.0;
