@@ -233,3 +233,26 @@ def test_tile_tuning_keeps_results_and_reports_a_time(tb, torch_cuda, oracle):
     check(oracle, got, oracle.host_conv2d(x, filt, 1, 1))
     got = device_conv(tb, torch_cuda, f, x[:3], 1, 1, 0)  # another shape: falls back to the model
     check(oracle, got, oracle.host_conv2d(x[:3], filt, 1, 1))
+
+
+def test_auto_choice_reports_the_kernel_an_automatic_launch_uses(tb, torch_cuda, oracle):
+    """tetris_conv2d_choice: a layer outside the tensor-core variant's cover (in_channel not a
+    multiple of 4) stays on the list kernel; a dense-ish 3x3 layer is given to the tensor cores
+    by the cost model; whatever is reported, the automatic launch gives the right answer."""
+    rng = np.random.default_rng(41)
+    filt3 = rng.normal(0, 0.05, (32, 3, 3, 3)).astype(np.float32)
+    f3 = tb.SparseFilter(filt3, 3, 32, 3)
+    assert tb.auto_choice(f3, 2, 32, 32, 1, 1) == tb.VARIANT_TILED
+    filt = rng.normal(0, 0.05, (128, 128, 3, 3)).astype(np.float32)
+    filt[rng.random(filt.shape) < 0.5] = 0
+    f = tb.SparseFilter(filt, 128, 128, 3)
+    x = rng.random((4, 128, 28, 28), dtype=np.float32)
+    choice = tb.auto_choice(f, 4, 28, 28, 1, 1)
+    assert choice == tb.VARIANT_TENSOR
+    got = device_conv(tb, torch_cuda, f, x, 1, 1, 0)
+    check(oracle, got, oracle.host_conv2d(x, filt, 1, 1))
+    # after tuning the answer is whichever kernel was faster when timed; it must be one of the two
+    xin = torch_cuda.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
+    out = torch_cuda.empty(4, 28, 28, 128, device="cuda")
+    tb.tune_sparse_conv2d(f, xin, out, 4, 28, 28, 1, 1, max_candidates=4)
+    assert tb.auto_choice(f, 4, 28, 28, 1, 1) in (tb.VARIANT_TILED, tb.VARIANT_TENSOR)

@@ -78,11 +78,6 @@ __device__ __forceinline__ float2 lds_f2(uint32_t a) {
   asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
   return v;
 }
-__device__ __forceinline__ uint2 lds_u2(uint32_t a) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-  return v;
-}
 __device__ __forceinline__ uint4 lds_u4(uint32_t a) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
