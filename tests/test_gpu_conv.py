@@ -256,3 +256,25 @@ def test_auto_choice_reports_the_kernel_an_automatic_launch_uses(tb, torch_cuda,
     out = torch_cuda.empty(4, 28, 28, 128, device="cuda")
     tb.tune_sparse_conv2d(f, xin, out, 4, 28, 28, 1, 1, max_candidates=4)
     assert tb.auto_choice(f, 4, 28, 28, 1, 1) in (tb.VARIANT_TILED, tb.VARIANT_TENSOR)
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_tensor_variant_random_shapes(tb, torch_cuda, oracle, seed):
+    """Ragged shapes for the tensor-core variant: channel counts that leave partial K chunks and
+    partial channel tiles, filters of 1 to 7 taps a side, strides 1-3, images smaller than a
+    tile, batches that share a tile, outputs that are not a multiple of four channels."""
+    rng = np.random.default_rng(1000 + seed)
+    ks = int(rng.choice([1, 2, 3, 5, 7]))
+    stride = int(rng.choice([1, 1, 2, 3]))
+    pad = int(rng.integers(0, ks))
+    ic = 4 * int(rng.integers(1, 40))
+    oc = int(rng.choice([1, 3, 30, 64, 65, 130, 200]))
+    h = int(rng.integers(ks, 40))
+    w = int(rng.integers(ks, 40))
+    n = int(rng.integers(1, 6))
+    filt = rng.normal(0, 0.05, (oc, ic, ks, ks)).astype(np.float32)
+    filt[rng.random(filt.shape) < rng.choice([0.0, 0.7, 0.95])] = 0
+    x = rng.random((n, ic, h, w), dtype=np.float32) - 0.3
+    f = tb.SparseFilter(filt, ic, oc, ks)
+    got = device_conv(tb, torch_cuda, f, x, stride, pad, VARIANTS["tensor"])
+    check(oracle, got, oracle.host_conv2d(x, filt, stride, pad))
