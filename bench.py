@@ -192,6 +192,8 @@ def main():
     ap.add_argument("--no-tune", action="store_true", help="skip the untimed tile auto-tuning pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="also time the step replayed as one CUDA graph (reported as `cuda_graph`)")
     args = ap.parse_args()
 
     tb = load_package()
@@ -230,13 +232,14 @@ def main():
             l["variant"] = 0
     torch.cuda.synchronize()
 
-    def launch_all(events=None):
+    def launch_all(events=None, st=None):
+        st = st or stream
         for i, l in enumerate(layers):
             L = l["L"]
             tb.sparse_conv2d(l["f"], l["x"], l["y"], args.batch, L.H, L.W, L.stride, L.pad,
-                             cuda_stream=stream, variant=l["variant"])
+                             cuda_stream=st, variant=l["variant"])
             if events is not None:
-                events[i + 1].record(stream)
+                events[i + 1].record(st)
 
     def barrier():
         torch.cuda.synchronize()
@@ -282,6 +285,30 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_per_step = float(t.item()) / args.steps
+
+    # ---- the same step as one CUDA graph (all layer launches captured once, replayed): what a
+    #      layer chain costs without the per-launch host work; an extra figure, not `value` ----
+    graph_info = None
+    if args.graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            launch_all(st=torch.cuda.current_stream())
+        for _ in range(args.warmup):
+            g.replay()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(args.steps):
+            g.replay()
+        g1.record()
+        barrier()
+        for l in layers:
+            l["f"].check()
+        tg = torch.tensor([g0.elapsed_time(g1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        gms = float(tg.item()) / args.steps
+        graph_info = {"ms_per_step": gms, "images_per_s": args.batch * world / (gms * 1e-3)}
     value = args.batch * world / (ms_per_step * 1e-3)
 
     # ---- end to end: host buffers in, host buffers out, through the host-pointer entry point ----
@@ -419,7 +446,7 @@ def main():
         "gpu_launches": args.steps * len(layers), "clocks": clocks,
         "model_roofline_frac": t_roof_sum / (sum(layer_ms) * 1e-3),
         "step_ms_min_max": [min(step_ms), max(step_ms)],
-        "cudnn_context": cudnn,
+        "cudnn_context": cudnn, "cuda_graph": graph_info,
         "per_layer": per_layer,
     }))
     if world > 1:

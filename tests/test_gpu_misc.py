@@ -67,3 +67,41 @@ def test_pipelined_host_path_equals_the_blocking_one(tb, torch_cuda, oracle):
     with pytest.raises(tb.TetrisError):
         tb.cuda_sparse_conv2d_async(xs[0], f, 3, 16, 16, 1, 1, outs[0], slot=9)
     tb.release_workspace()
+
+
+@pytest.mark.gpu
+def test_layer_chain_replays_from_a_cuda_graph(tb, torch_cuda, oracle):
+    """Two layers back to back (list kernel, then the tensor-core variant with its split-K
+    zeroing), captured once into a CUDA graph and replayed: same results as the eager launches."""
+    torch = torch_cuda
+    rng = np.random.default_rng(5)
+    f1w = rng.normal(0, 0.05, (64, 8, 3, 3)).astype(np.float32)
+    f1w[rng.random(f1w.shape) < 0.8] = 0
+    f2w = rng.normal(0, 0.05, (96, 64, 3, 3)).astype(np.float32)
+    f2w[rng.random(f2w.shape) < 0.8] = 0
+    f1, f2 = tb.SparseFilter(f1w, 8, 64, 3), tb.SparseFilter(f2w, 64, 96, 3)
+    x = rng.random((2, 8, 20, 20), dtype=np.float32)
+    xin = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
+    mid = torch.zeros(2, 20, 20, 64, device="cuda")
+    out = torch.zeros(2, 20, 20, 96, device="cuda")
+
+    def chain(st):
+        tb.sparse_conv2d(f1, xin, mid, 2, 20, 20, 1, 1, cuda_stream=st, variant=tb.VARIANT_TILED)
+        tb.sparse_conv2d(f2, mid, out, 2, 20, 20, 1, 1, cuda_stream=st, variant=tb.VARIANT_TENSOR)
+
+    chain(torch.cuda.current_stream())       # eager once: one-time set-up happens outside the capture
+    torch.cuda.synchronize()
+    want = out.clone()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        chain(torch.cuda.current_stream())
+    out.fill_(float("nan"))
+    mid.fill_(float("nan"))
+    g.replay()
+    torch.cuda.synchronize()
+    f2.check()
+    assert torch.allclose(out, want, rtol=1e-5, atol=1e-6)
+    y1 = oracle.host_conv2d(x, f1w, 1, 1)
+    y2 = oracle.host_conv2d(y1, f2w, 1, 1)
+    bad, _, _ = oracle.compare(out.cpu().numpy().transpose(0, 3, 1, 2), y2)
+    assert bad == 0
