@@ -458,6 +458,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     const int row = quarter * 32 + lane;   // tile row = pixel = TMEM lane
     const int pw = row % p.TW, ph = (row / p.TW) % p.TH, pn = row / (p.TW * p.TH);
     const bool vec = (p.OC & 3) == 0;
+    const bool vec8 = (p.OC & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
     int cbase = 0, sp = 0;  // first group of the tile; partial sum, counted across tiles
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, cbase += tile_groups) {
@@ -500,6 +501,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           for (int j = 0; j < NC; ++j)
             if (ocb + j < p.OC) atomicAdd(o + j, acc[j]);
         }
+      } else if (vec8 && ocb + NC <= p.OC) {
+        // 32 bytes per lane: the 32 lanes of a store write 32 different lines either way, so
+        // wider stores halve the passes through the memory pipe, which the tile's stores
+        // otherwise hold for ~4000 clocks while the converter warps queue behind them
+#pragma unroll
+        for (int j = 0; j < NC; j += 8)
+          asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(o + j), "f"(acc[j]), "f"(acc[j + 1]), "f"(acc[j + 2]), "f"(acc[j + 3]),
+                       "f"(acc[j + 4]), "f"(acc[j + 5]), "f"(acc[j + 6]), "f"(acc[j + 7]) : "memory");
       } else if (vec && ocb + NC <= p.OC) {
 #pragma unroll
         for (int j = 0; j < NC; j += 4) *reinterpret_cast<float4 *>(o + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
