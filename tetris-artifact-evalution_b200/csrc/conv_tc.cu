@@ -35,7 +35,7 @@
 //     a box per tap moves 6x the bytes, and 128-byte rows scattered over L2 come in at only
 //     ~25 B/clock/SM (measured), which made the activation loads as slow as the MMAs;
 //   * warp 2 (one thread): one bulk copy per K step of a prepared {w_hi, w_lo} tile image into
-//     a 5-deep ring;
+//     a 4-deep ring;
 //   * warps 4-11: per K step read the patch rows of the tap (un-swizzling) and write
 //     x_hi = tf32(x) and x_lo = tf32(x - x_hi) into a 4-deep ring of 64 TMEM columns
 //     (tcgen05.st); warps 4-7 take the even K steps, warps 8-11 the odd ones, because one
@@ -49,8 +49,8 @@
 //     partial accumulator over;
 //   * warps 12-19: read the partial accumulator (tcgen05.ld; a warp may touch the TMEM lanes
 //     of its quarter, two warps share a quarter and take half of the channels each), release
-//     it, add it to the running sum; after the tile's last K step store the sums, 256
-//     contiguous bytes per thread (NHWC).
+//     it, add it to the running sum; after the tile's last K step turn the sums through a
+//     4 KiB staging block per warp so that eight lanes store one pixel's 128 contiguous bytes.
 // Every barrier wait is bounded: on a timeout an error flag is raised, all roles drain, TMEM is
 // freed and the kernel returns; the host reports TETRIS_ERR_CUDA.
 //
