@@ -463,7 +463,23 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     const int pw = row % p.TW, ph = (row / p.TW) % p.TH, pn = row / (p.TW * p.TH);
     const bool vec = (p.OC & 3) == 0;
     const bool vec8 = (p.OC & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
+    const bool small_out = (unsigned long long)p.N * p.OH * p.OW * p.OC < (1ull << 34);  // 32-bit offsets in 16-byte units
     int cbase = 0, sp = 0;  // first group of the tile; partial sum, counted across tiles
+    // Item t = blockIdx.x + k * gridDim.x in mixed radix (K slice, channel tile, tile column,
+    // tile row, image group): decoded once here and advanced by digit-wise addition per item
+    // (eight divisions per item cost this warp ~900 clocks, measured, and on short-K layers
+    // these warps set the pace).
+    const int radix[4] = {p.ksplit, oc_tiles, p.tiles_w, p.tiles_h};
+    int cur[5], step[5];
+    {
+      int a = blockIdx.x, b2 = gridDim.x;
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        cur[d] = a % radix[d]; a /= radix[d];
+        step[d] = b2 % radix[d]; b2 /= radix[d];
+      }
+      cur[4] = a; step[4] = b2;
+    }
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, cbase += tile_groups) {
       float acc[NC];
@@ -489,13 +505,23 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         }
       }
       if (!ok) break;
-      int w0, h0, n0, oc0, chunk0;
-      decode(t, w0, h0, n0, oc0, chunk0);
+      // the item's tile coordinates, counted along in mixed radix (see `step` below)
+      const int w0 = cur[2] * p.TW, h0 = cur[3] * p.TH, n0 = cur[4] * p.NB, oc0 = cur[1] * BN;
+      {
+        int carry = 0;
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+          cur[d] += step[d] + carry;
+          carry = cur[d] >= radix[d] ? 1 : 0;
+          cur[d] -= carry ? radix[d] : 0;
+        }
+        cur[4] += step[4] + carry;
+      }
       const int ow = w0 + pw, oh = h0 + ph, n = n0 + pn;
       const bool row_ok = pn < p.NB && ow < p.OW && oh < p.OH && n < p.N && !*abort_flag;
       const int ocb = oc0 + half * NC;
       float *o = p.out + (((size_t)n * p.OH + oh) * p.OW + ow) * p.OC + ocb;
-      if (vec && ocb + NC <= p.OC) {
+      if (vec && ocb + NC <= p.OC && small_out) {
         // Coalesced path.  A thread holds 32..64 channels of ONE pixel, so stored directly the
         // 32 lanes of an instruction hit 32 different lines (32 passes through the memory pipe
         // per instruction, 2048 per tile, and the converter warps' traffic queues behind
@@ -503,6 +529,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         // block per warp the rows are turned so that eight lanes write one pixel's 128
         // contiguous bytes: 4 passes per instruction, 512 per tile.
         float4 *stage = reinterpret_cast<float4 *>(store_base + (warp - 12) * 4096);
+        // this thread's pixel as an offset into the output in 16-byte units (invalid: all ones)
+        const uint32_t off16 = row_ok ? (uint32_t)((o - p.out) >> 2) : 0xFFFFFFFFu;
 #pragma unroll
         for (int h = 0; h < NC / 32; ++h) {
 #pragma unroll
@@ -510,18 +538,24 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
             stage[lane * 8 + (qq ^ (lane & 7))] = make_float4(acc[h * 32 + 4 * qq], acc[h * 32 + 4 * qq + 1],
                                                                acc[h * 32 + 4 * qq + 2], acc[h * 32 + 4 * qq + 3]);
           __syncwarp();
+          // all loads first: a store through a generic pointer may alias the staging block as far
+          // as the compiler knows, which would serialise load, store, load, ...
+          float4 v[8];
+          const int qq = lane & 7;
 #pragma unroll
-          for (int r0 = 0; r0 < 32; r0 += 4) {
-            const int r = r0 + (lane >> 3), qq = lane & 7;
-            const float4 v = stage[r * 8 + (qq ^ (r & 7))];
-            const unsigned long long optr = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(o), r);
-            const int okr = __shfl_sync(0xffffffffu, row_ok ? 1 : 0, r);
-            float *dst = reinterpret_cast<float *>(optr) + h * 32 + 4 * qq;
-            if (okr) {
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + (lane >> 3);
+            v[i] = stage[r * 8 + (qq ^ (r & 7))];
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t off = __shfl_sync(0xffffffffu, off16, 4 * i + (lane >> 3));
+            float *dst = p.out + ((size_t)off << 2) + h * 32 + 4 * qq;
+            if (off != 0xFFFFFFFFu) {
               if (p.ksplit > 1)  // a slice of the K range: add into the zeroed output
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v[i].x), "f"(v[i].y), "f"(v[i].z), "f"(v[i].w) : "memory");
               else
-                *reinterpret_cast<float4 *>(dst) = v;
+                *reinterpret_cast<float4 *>(dst) = v[i];
             }
           }
           __syncwarp();
