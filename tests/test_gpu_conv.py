@@ -31,11 +31,11 @@ def device_conv(tb, torch, f, x_nchw, stride, pad, variant=0, poison=True):
 
 def covers(variant, ks, stride, ic=4):
     """The interpreter kernel is instantiated for 1x1 and 3x3, stride 1 and 2 only; the
-    tensor-core variant needs in_channel to be a multiple of 4."""
+    tensor-core variant needs in_channel to be a multiple of 4, or at most 4."""
     if variant == "interp":
         return ks in (1, 3) and stride in (1, 2)
     if variant == "tensor":
-        return ic % 4 == 0
+        return ic % 4 == 0 or ic <= 4
     return True
 
 
@@ -237,11 +237,11 @@ def test_tile_tuning_keeps_results_and_reports_a_time(tb, torch_cuda, oracle):
 
 def test_auto_choice_reports_the_kernel_an_automatic_launch_uses(tb, torch_cuda, oracle):
     """tetris_conv2d_choice: a layer outside the tensor-core variant's cover (in_channel not a
-    multiple of 4) stays on the list kernel; a dense-ish 3x3 layer is given to the tensor cores
+    multiple of 4 and more than 4) stays on the list kernel; a dense-ish 3x3 layer is given to the tensor cores
     by the cost model; whatever is reported, the automatic launch gives the right answer."""
     rng = np.random.default_rng(41)
-    filt3 = rng.normal(0, 0.05, (32, 3, 3, 3)).astype(np.float32)
-    f3 = tb.SparseFilter(filt3, 3, 32, 3)
+    filt3 = rng.normal(0, 0.05, (32, 6, 3, 3)).astype(np.float32)
+    f3 = tb.SparseFilter(filt3, 6, 32, 3)
     assert tb.auto_choice(f3, 2, 32, 32, 1, 1) == tb.VARIANT_TILED
     filt = rng.normal(0, 0.05, (128, 128, 3, 3)).astype(np.float32)
     filt[rng.random(filt.shape) < 0.5] = 0
@@ -267,7 +267,7 @@ def test_tensor_variant_random_shapes(tb, torch_cuda, oracle, seed):
     ks = int(rng.choice([1, 2, 3, 5, 7]))
     stride = int(rng.choice([1, 1, 2, 3]))
     pad = int(rng.integers(0, ks))
-    ic = 4 * int(rng.integers(1, 40))
+    ic = int(rng.choice([1, 2, 3])) if seed % 3 == 0 else 4 * int(rng.integers(1, 40))
     oc = int(rng.choice([1, 3, 30, 64, 65, 130, 200]))
     h = int(rng.integers(ks, 40))
     w = int(rng.integers(ks, 40))

@@ -98,6 +98,10 @@ struct TcParams {
   int TW, TH, NB;              // pixels of a tile: TW x TH x NB <= 128 rows
   int PW, PH;                  // the tile with its halo: PW = TW + KS - 1, PH = TH + KS - 1
   int per_tap, S;              // per_tap: one strided box per K step instead of a patch per chunk (stride > 1)
+  int folded;                  // <= 4 input channels: K = (filter row, filter column, channel) folded into
+                               // 32-wide chunks, activations gathered from global memory by the converters
+  const float *in;             // activations (folded mode only)
+  int H, W, IC;                // input extent (folded mode only)
   int tiles_w, tiles_h, tiles_n;
   int n_chunks;                // ceil(IC / 32)
   int ksplit;                  // work items per tile: each takes n_chunks / ksplit chunks and adds its result in
@@ -229,7 +233,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
 
   // Persistent CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the channel tile is the
   // fastest index, so CTAs that run side by side read the same activation patch.
-  const int taps = p.KS * p.KS;
+  const int taps = p.folded ? 1 : p.KS * p.KS;  // K steps per channel chunk
   const int item_chunks = p.n_chunks / p.ksplit;            // chunks of a work item (ksplit divides n_chunks)
   const int iters = taps * item_chunks;                     // K steps of a work item
   const int tile_groups = (iters + kPromote - 1) / kPromote;  // groups of a tile
@@ -260,7 +264,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     if (lane == 0) {
       int u = 0;  // loads of this CTA, across tiles
       bool ok = true;
-      if (!p.per_tap) {
+      if (p.folded) {
+        // the converters gather the activations themselves
+      } else if (!p.per_tap) {
         // One patch per 32-channel chunk: the tile plus its halo, shared by all taps.
         const uint32_t x_box_bytes = (uint32_t)(p.PW * p.PH * p.NB * KC * 4);
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -395,9 +401,43 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     // converters' own instruction count is on the critical path).
     int g = 0, u = 0;                        // K step and patch of this CTA, counted across tiles
     int seen_u = -1;                         // patch this warp has already waited for
+    // folded mode: this thread's pixel per item, item coordinates counted along in mixed radix
+    const int radix[4] = {p.ksplit, oc_tiles, p.tiles_w, p.tiles_h};
+    int cur[5] = {0, 0, 0, 0, 0}, step[5] = {0, 0, 0, 0, 0};
+    if (p.folded) {
+      int a = blockIdx.x, b2 = gridDim.x;
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        cur[d] = a % radix[d]; a /= radix[d];
+        step[d] = b2 % radix[d]; b2 /= radix[d];
+      }
+      cur[4] = a; step[4] = b2;
+    }
+    const int fold_row = p.KS * p.IC, fold_k = p.KS * fold_row;       // floats per filter row / per filter
+    const uint32_t rcp_row = 65536u / (uint32_t)max(fold_row, 1) + 1u;  // exact quotients for indices < 256
+    const uint32_t rcp_ic = 65536u / (uint32_t)max(p.IC, 1) + 1u;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int tap = 0, r = 0, q = 0;
+      // folded mode: input position of this thread's pixel for filter tap (0, 0)
+      int f_ih0 = 0, f_iw0 = 0, f_chunk0 = 0;
+      const float *f_img = nullptr;
+      bool f_live = false;
+      if (p.folded) {
+        const int n = cur[4] * p.NB + pn, oh = cur[3] * p.TH + ph, ow = cur[2] * p.TW + pw;
+        f_chunk0 = cur[0] * item_chunks;
+        f_live = live && n < p.N && oh < p.OH && ow < p.OW;
+        f_ih0 = oh * p.S - p.P; f_iw0 = ow * p.S - p.P;
+        f_img = p.in + (size_t)(f_live ? n : 0) * p.H * p.W * p.IC;
+        int carry = 0;
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+          cur[d] += step[d] + carry;
+          carry = cur[d] >= radix[d] ? 1 : 0;
+          cur[d] -= carry ? radix[d] : 0;
+        }
+        cur[4] += step[4] + carry;
+      }
       for (int it = 0; it < iters; ++it, ++g) {
         const int sa = g % kAStages;
         // activation stage, its phase, and whether this K step is the last to read it
@@ -407,17 +447,31 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         if ((g & 1) == set) {
           // Read and split this tap's rows first: everything up to the tensor-memory store can
           // be done while the operand stage is still in use.
+          uint32_t hi[32], lo[32];
+          if (p.folded) {
+            // K index k = (filter row, filter column, channel): within a filter row the
+            // (column, channel) pairs are contiguous in the NHWC input, so element k of this
+            // pixel is img[(ih0 + row) * W * IC + iw0 * IC + rem] where it exists.
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const uint32_t k = (uint32_t)((f_chunk0 + it) * KC + c);
+              const uint32_t fr = (k * rcp_row) >> 16, rem = k - fr * (uint32_t)fold_row;
+              const int ih = f_ih0 + (int)fr, iw = f_iw0 + (int)((rem * rcp_ic) >> 16);
+              const bool inside = f_live && (int)k < fold_k && ih >= 0 && ih < p.H && iw >= 0 && iw < p.W;
+              hi[c] = inside ? __float_as_uint(__ldg(f_img + ((long long)ih * p.W + f_iw0) * p.IC + (int)rem)) : 0u;
+            }
+          } else {
           if (p.per_tap || seen_u != u) {  // a patch is waited for once, at the first tap this warp reads
             if (!(ok = mbar_wait_warp(bar_xfull(sx), xphase, abort_flag, lane))) break;
             seen_u = u;
           }
           const int prow = p.per_tap ? row : live ? prow0 + r * p.PW + q : 0;
           const unsigned char *src = xbase + (p.per_tap ? sx * kTileBytes : sx * kPatchBytes) + prow * 128;
-          uint32_t hi[32], lo[32];
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             const uint4 v = *reinterpret_cast<const uint4 *>(src + ((c ^ (prow & 7)) << 4));
             hi[4 * c + 0] = v.x; hi[4 * c + 1] = v.y; hi[4 * c + 2] = v.z; hi[4 * c + 3] = v.w;
+          }
           }
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
@@ -438,7 +492,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           __syncwarp();
           if (lane == 0) {
             mbar_arrive(bar_afull(sa));
-            if (p.per_tap) mbar_arrive(bar_xempty(sx));  // a per-tap box has this one reader set
+            if (p.per_tap && !p.folded) mbar_arrive(bar_xempty(sx));  // a per-tap box has this one reader set
           }
         }
         // The patch is released by every warp once its own last K step of the chunk is behind
@@ -446,7 +500,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         // waits, produced wrong results on the 56x56 and 112x112 layers.)
         if (last_of_chunk) {
           __syncwarp();
-          if (lane == 0 && !p.per_tap) mbar_arrive(bar_xempty(sx));
+          if (lane == 0 && !p.per_tap && !p.folded) mbar_arrive(bar_xempty(sx));
           ++u;
           tap = 0; r = 0; q = 0;
         } else {
@@ -602,20 +656,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
 // 128-byte-swizzled order the tensor core reads (16-byte chunk j of row r sits at chunk
 // j ^ (r & 7)), so that one contiguous bulk copy fills a stage.  Channels past IC or OC are zero.
 __global__ void tc_weight_tiles_kernel(const float *__restrict__ filt, float *__restrict__ tiles,
-                                       int OC, int IC, int KS, int n_chunks, int oc_tiles, int BN) {
-  const long long total = (long long)KS * KS * n_chunks * oc_tiles * 2 * BN * KC;
+                                       int OC, int IC, int KS, int n_chunks, int oc_tiles, int BN, int folded) {
+  const long long total = (long long)(folded ? 1 : KS * KS) * n_chunks * oc_tiles * 2 * BN * KC;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int col = (int)(i % KC);
     const int row = (int)((i / KC) % BN);
     const int half = (int)((i / ((long long)KC * BN)) % 2);
     long long tile = i / ((long long)2 * KC * BN);
     const int oct = (int)(tile % oc_tiles); tile /= oc_tiles;
-    const int tap = (int)(tile % (KS * KS));  // K steps run chunk-major, tap-minor
-    const int chunk = (int)(tile / (KS * KS));
     const int k = (((col >> 2) ^ (row & 7)) << 2) | (col & 3);
-    const int ic = chunk * KC + k, oc = oct * BN + row;
+    const int oc = oct * BN + row;
     float w = 0.f;
-    if (ic < IC && oc < OC) w = filt[((size_t)oc * IC + ic) * KS * KS + tap];
+    if (folded) {  // K index = (filter row, filter column, channel), cut into chunks of 32
+      const int kk = (int)tile * KC + k;
+      const int tap = kk / IC, ic = kk - tap * IC;
+      if (tap < KS * KS && oc < OC) w = filt[((size_t)oc * IC + ic) * KS * KS + tap];
+    } else {
+      const int tap = (int)(tile % (KS * KS));  // K steps run chunk-major, tap-minor
+      const int chunk = (int)(tile / (KS * KS));
+      const int ic = chunk * KC + k;
+      if (ic < IC && oc < OC) w = filt[((size_t)oc * IC + ic) * KS * KS + tap];
+    }
     const float h = __uint_as_float(round_tf32(w));
     tiles[i] = half ? __uint_as_float(round_tf32(w - h)) : h;
   }
@@ -651,6 +712,7 @@ struct TcState {
   float *d_tiles = nullptr;  // weight tile images
   int *d_error = nullptr;
   int n_chunks = 0, bn = 128;  // K chunks per tap; channel tile (fixed by the filter: 64 up to 64 channels)
+  bool folded = false;         // <= 4 input channels: taps and channels folded into one K axis
   // activation map of the last input pointer / shape
   std::mutex mutex;
   const float *last_in = nullptr;
@@ -673,14 +735,16 @@ void conv_tc_state_delete(void *state) {
 // the OIHW filter on the device).  Failure here is not fatal for the filter: the variant is then
 // reported as unsupported.
 int conv_tc_prepare(tetris_filter *f, const float *d_dense) {
-  if (f->groups != 1 || (f->in_channel & 3) != 0) return TETRIS_OK;  // not covered: leave tc_state null
+  const bool folded = f->in_channel <= 4;
+  if (f->groups != 1 || (!folded && (f->in_channel & 3) != 0)) return TETRIS_OK;  // not covered: leave tc_state null
   TcState *s = new (std::nothrow) TcState();
   if (!s) return TETRIS_OK;
   const int KS = f->kernel_size, taps = KS * KS;
-  s->n_chunks = (f->in_channel + KC - 1) / KC;
+  s->folded = folded;
+  s->n_chunks = folded ? (taps * f->in_channel + KC - 1) / KC : (f->in_channel + KC - 1) / KC;
   s->bn = f->out_channel <= 64 ? 64 : 128;
   const int oc_tiles = (f->out_channel + s->bn - 1) / s->bn;
-  const size_t elems = (size_t)taps * s->n_chunks * oc_tiles * 2 * s->bn * KC;
+  const size_t elems = (size_t)(folded ? 1 : taps) * s->n_chunks * oc_tiles * 2 * s->bn * KC;
   if (cudaMalloc(&s->d_tiles, elems * 4) != cudaSuccess || cudaMalloc(&s->d_error, sizeof(int)) != cudaSuccess) {
     cudaGetLastError();
     conv_tc_state_delete(s);
@@ -688,7 +752,7 @@ int conv_tc_prepare(tetris_filter *f, const float *d_dense) {
   }
   cudaMemset(s->d_error, 0, sizeof(int));
   tc_weight_tiles_kernel<<<(unsigned)std::min<size_t>((elems + 255) / 256, 4096), 256>>>(
-      d_dense, s->d_tiles, f->out_channel, f->in_channel, KS, s->n_chunks, oc_tiles, s->bn);
+      d_dense, s->d_tiles, f->out_channel, f->in_channel, KS, s->n_chunks, oc_tiles, s->bn, folded ? 1 : 0);
   if (cudaGetLastError() != cudaSuccess) {
     conv_tc_state_delete(s);
     return TETRIS_OK;
@@ -699,16 +763,16 @@ int conv_tc_prepare(tetris_filter *f, const float *d_dense) {
 
 bool conv_tc_supported(const tetris_filter *f, const ConvShape &s) {
   if (!f->tc_state || f->groups != 1) return false;
-  if (s.S < 1 || s.S > 8 || (s.IC & 3) != 0 || s.N < 1 || s.OH < 1 || s.OW < 1) return false;
-  return true;
+  if (s.S < 1 || s.S > 8 || s.N < 1 || s.OH < 1 || s.OW < 1) return false;
+  return static_cast<TcState *>(f->tc_state)->folded || (s.IC & 3) == 0;
 }
 
 int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const ConvShape &s, cudaStream_t st) {
-  if (!conv_tc_supported(f, s) || (reinterpret_cast<uintptr_t>(in) & 15) != 0) {
-    set_error("tensor-core variant covers strides up to 8, in_channel %% 4 == 0 and 16-byte aligned inputs only");
+  TcState *t = static_cast<TcState *>(f->tc_state);
+  if (!conv_tc_supported(f, s) || (!t->folded && (reinterpret_cast<uintptr_t>(in) & 15) != 0)) {
+    set_error("tensor-core variant covers strides up to 8, in_channel <= 4 or a multiple of 4, 16-byte aligned inputs");
     return TETRIS_ERR_UNSUPPORTED;
   }
-  TcState *t = static_cast<TcState *>(f->tc_state);
   CUtensorMap map_x;
   TcParams p;
   dim3 grid;
@@ -721,14 +785,14 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
       // pixels of a tile: TW x TH x NB rows, at most 128, as full as possible, and -- at stride
       // 1, where all taps read one patch -- such that the tile with its halo fits a stage
       // (1x1 filters have no halo to share either, and the per-K-step ring is four deep)
-      const bool per_tap = s.S > 1 || s.KS == 1;
+      const bool per_tap = s.S > 1 || s.KS == 1 || t->folded;
       const int halo = per_tap ? 0 : s.KS - 1;
       int best_tw = 0, best_th = 1, best_nb = 1;
       double best = -1.0;
       for (int TW = 1; TW <= std::min(s.OW, 128); ++TW) {
         int TH = std::min(s.OH, 128 / TW);
         while (TH > 1 && (TW + halo) * (TH + halo) > kPatchRows) --TH;
-        if (TH < 1 || (TW + halo) * (TH + halo) > kPatchRows || TW * s.S > 256 || TH * s.S > 256) continue;
+        if (TH < 1 || (TW + halo) * (TH + halo) > kPatchRows || (!t->folded && (TW * s.S > 256 || TH * s.S > 256))) continue;
         int NB = (TH == s.OH && TW == s.OW) ? std::min(s.N, 128 / (TW * TH)) : 1;
         while (NB > 1 && (TW + halo) * (TH + halo) * NB > kPatchRows) --NB;
         const double tiles = (double)((s.OW + TW - 1) / TW) * ((s.OH + TH - 1) / TH) * ((s.N + NB - 1) / NB);
@@ -745,13 +809,16 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
       // with element strides the box spans S times the pixels it loads
       const cuuint32_t box[4] = {KC, (cuuint32_t)(PW * s.S), (cuuint32_t)(PH * s.S), (cuuint32_t)best_nb};
       const cuuint32_t estr[4] = {1, (cuuint32_t)s.S, (cuuint32_t)s.S, 1};
-      const int rc = encode_map(&t->map_x, const_cast<float *>(in), 4, dims, strides, box, estr);
-      if (rc) return rc;
+      if (!t->folded) {  // (folded mode reads the activations with plain loads)
+        const int rc = encode_map(&t->map_x, const_cast<float *>(in), 4, dims, strides, box, estr);
+        if (rc) return rc;
+      }
       TcParams &q = t->params;
       q.N = s.N; q.OH = s.OH; q.OW = s.OW; q.OC = s.OC; q.P = s.P; q.KS = s.KS;
       q.TW = best_tw; q.TH = best_th; q.NB = best_nb;
       q.PW = PW; q.PH = PH;
       q.per_tap = per_tap ? 1 : 0; q.S = s.S;
+      q.folded = t->folded ? 1 : 0; q.in = in; q.H = s.H; q.W = s.W; q.IC = s.IC;
       q.tiles_w = (s.OW + best_tw - 1) / best_tw;
       q.tiles_h = (s.OH + best_th - 1) / best_th;
       q.tiles_n = (s.N + best_nb - 1) / best_nb;
@@ -767,7 +834,7 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
       // waves x (K steps + ~10 for filling and draining the pipeline per item), plus zeroing
       // the output that the items add into.  Measured on 28x28x512 -> 512: 0.396 ms unsplit,
       // 0.357 ms in two slices, 0.349 ms in four.
-      const double iters = (double)s.KS * s.KS * q.n_chunks;
+      const double iters = (double)(t->folded ? 1 : s.KS * s.KS) * q.n_chunks;
       const double zeroing = ((double)s.N * s.OH * s.OW * s.OC * 4 / 6.0e12 + 3e-6) * 1.9e9 / 1450.0;
       int best_d = 1;
       double best_cost = std::ceil((double)tiles / sms) * (iters + 10.0);

@@ -423,7 +423,8 @@ void fill_plan(const tetris_filter *f, const ConvShape &s, const Candidate &c, i
 // 128x128x8 plus operand traffic), plus prologue and epilogue, in waves of one CTA per SM.
 double tc_cost(const tetris_filter *f, const ConvShape &s, int sm_count) {
   const double tiles = std::ceil((double)s.N * s.OH * s.OW / 128.0 / 0.9) * ((s.OC + 127) / 128);
-  const double iters = (double)s.KS * s.KS * ((s.IC + 31) / 32);
+  // (up to 4 input channels the variant folds taps and channels into one K axis)
+  const double iters = s.IC <= 4 ? (double)((s.KS * s.KS * s.IC + 31) / 32) : (double)s.KS * s.KS * ((s.IC + 31) / 32);
   return std::ceil(tiles / sm_count) * (iters * 1500.0 + 8000.0);  // measured clocks per K step and per tile
 }
 
