@@ -56,7 +56,8 @@ enum {
   TETRIS_VARIANT_INTERP = 3,  /* shared-memory tile, jump-table interpreter that reuses a
                                  register-resident input window across channels (1x1, 3x3) */
   TETRIS_VARIANT_TENSOR = 4   /* dense contraction on the tensor cores (tcgen05, split TF32);
-                                 strides 1-8, in_channel % 4 == 0, 16-byte aligned input  */
+                                 strides 1-8; in_channel <= 4, or a multiple of 4 with a
+                                 16-byte aligned input                                    */
 };
 
 typedef struct tetris_filter tetris_filter_t; /* opaque; owns device buffers */

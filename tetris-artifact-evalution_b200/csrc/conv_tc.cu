@@ -35,7 +35,7 @@
 //     a box per tap moves 6x the bytes, and 128-byte rows scattered over L2 come in at only
 //     ~25 B/clock/SM (measured), which made the activation loads as slow as the MMAs;
 //   * warp 2 (one thread): one bulk copy per K step of a prepared {w_hi, w_lo} tile image into
-//     a 4-deep ring;
+//     a 5-deep ring (4-deep on layers with few K steps per item, see w_stages);
 //   * warps 4-11: per K step read the patch rows of the tap (un-swizzling) and write
 //     x_hi = tf32(x) and x_lo = tf32(x - x_hi) into a 4-deep ring of 64 TMEM columns
 //     (tcgen05.st); warps 4-7 take the even K steps, warps 8-11 the odd ones, because one
@@ -58,8 +58,12 @@
 // falls back to one box per K step (the tile's input pixels of that tap, picked by the tensor
 // map's element strides) in a 4-deep ring of 16 KiB stages.
 //
-// No cluster launch: every load is issued by one CTA for itself.  Covers strides 1-8, IC % 4 == 0
-// (TMA needs 16-byte strides).
+// With at most 4 input channels (the stems of the networks) taps and channels are folded into
+// one K axis, K = KS*KS*IC in chunks of 32, and the converter warps gather the activations from
+// global memory themselves (TMA needs 16-byte strides; an NHWC pixel of 3 floats has 12).
+//
+// No cluster launch: every load is issued by one CTA for itself.  Covers strides 1-8, IC <= 4 or
+// IC % 4 == 0.
 #include <cuda.h>
 
 #include <algorithm>
@@ -73,16 +77,17 @@ namespace {
 
 constexpr int BM = 128, KC = 32;  // tile rows (pixels), K chunk (32 floats = 128 B); BN = 64 or 128 channels
 constexpr int kXStages = 4;                 // activation stages: 4 of 16 KiB (a box per K step) or 2 of 32 KiB (patches)
-constexpr int kWStages = 4;                 // ring of {w_hi, w_lo} tile pairs (shared memory, TMA target); a fifth
-                                            // stage measured 2-3 % faster on 3x3 layers, the store staging that
-                                            // takes its place 2x on short-K layers
+constexpr int kWStages = 5;                 // ring of {w_hi, w_lo} tile pairs (shared memory, TMA target); the
+                                            // fifth stage is given up for the store staging block on layers
+                                            // with few K steps per tile (TcParams::w_stages)
 constexpr int kAStages = 4;                 // ring of {x, x_lo} operand blocks (tensor memory)
 constexpr int kTileBytes = BM * KC * 4;     // 16 KiB: one 128-row x 128-byte operand tile
 constexpr int kPatchRows = 256;             // rows of 128 bytes an activation stage holds
 constexpr int kPatchBytes = kPatchRows * KC * 4;
 constexpr int kXBytes = 2 * kPatchBytes;     // shared memory of the activation ring, either way
 constexpr int kStoreBytes = 8 * 32 * 32 * 4;  // store staging: per summing warp 32 rows x 32 channels
-constexpr int kSmemTiles = kXBytes + kWStages * 2 * kTileBytes + kStoreBytes;
+constexpr int kSmemTiles = kXBytes + kWStages * 2 * kTileBytes;  // the store staging block lies over the fifth weight stage
+static_assert(kStoreBytes <= 2 * kTileBytes, "the store staging block must fit a weight stage");
 constexpr int kPromote = 2;                 // K steps per group: one commit, releases the operand stages
 constexpr int kSuper = 2;                   // groups accumulated on the tensor core before the FP32 add outside
 constexpr int kTmemCols = 512;              // 2 partial accumulators (<= 128 columns each) + 4 x 64 operand columns
@@ -98,6 +103,7 @@ struct TcParams {
   int TW, TH, NB;              // pixels of a tile: TW x TH x NB <= 128 rows
   int PW, PH;                  // the tile with its halo: PW = TW + KS - 1, PH = TH + KS - 1
   int per_tap, S;              // per_tap: one strided box per K step instead of a patch per chunk (stride > 1)
+  int w_stages;                // weight stages in use: 5, or 4 with the fifth as store staging block
   int folded;                  // <= 4 input channels: K = (filter row, filter column, channel) folded into
                                // 32-wide chunks, activations gathered from global memory by the converters
   const float *in;             // activations (folded mode only)
@@ -199,7 +205,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char *xbase = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
   unsigned char *wbase = xbase + kXBytes;
-  unsigned char *store_base = wbase + kWStages * 2 * kTileBytes;
+  unsigned char *store_base = wbase + 4 * 2 * kTileBytes;  // = weight stage 4, unused when w_stages == 4
   uint64_t *bars = reinterpret_cast<uint64_t *>(xbase + kSmemTiles);
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -306,8 +312,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         int w0, h0, n0, oc0, chunk0;
         decode(t, w0, h0, n0, oc0, chunk0);
         for (int it = 0; it < iters; ++it, ++g) {
-          const int s = g % kWStages;
-          if (g >= kWStages && !(ok = wait_group(group_of(g - kWStages)))) break;
+          const int s = g % p.w_stages;
+          if (g >= p.w_stages && !(ok = wait_group(group_of(g - p.w_stages)))) break;
           // K step `it` of channel tile oc0 / BN: one contiguous {w_hi, w_lo} image
           const float *src = p.w_tiles + ((size_t)(chunk0 * taps + it) * oc_tiles + oc0 / BN) * (2 * BN * KC);
           mbar_expect_tx(bar_wfull(s), (uint32_t)(2 * BN * KC * 4));
@@ -349,7 +355,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
             }
           }
           __syncwarp();
-          if (++sw == kWStages) sw = 0;
+          if (++sw == p.w_stages) sw = 0;
         }
         if (ok && elect_one()) umma_commit(bar_gdone(c % kGroups));  // arrives when the group's last MMA has completed
         __syncwarp();
@@ -381,7 +387,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
             if (!(ok = wait_group(cprev))) break;
           }
           mbar_arrive(bar_ready(g % kAStages));
-          if (++ws == kWStages) { ws = 0; wphase ^= 1u; }
+          if (++ws == p.w_stages) { ws = 0; wphase ^= 1u; }
         }
       }
     }
@@ -575,7 +581,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
       const bool row_ok = pn < p.NB && ow < p.OW && oh < p.OH && n < p.N && !*abort_flag;
       const int ocb = oc0 + half * NC;
       float *o = p.out + (((size_t)n * p.OH + oh) * p.OW + ow) * p.OC + ocb;
-      if (vec && ocb + NC <= p.OC && small_out) {
+      if (vec && ocb + NC <= p.OC && small_out && p.w_stages == 4) {
         // Coalesced path.  A thread holds 32..64 channels of ONE pixel, so stored directly the
         // 32 lanes of an instruction hit 32 different lines (32 passes through the memory pipe
         // per instruction, 2048 per tile, and the converter warps' traffic queues behind
@@ -844,6 +850,9 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
         if (cost < 0.96 * best_cost) { best_cost = cost; best_d = d; }
       }
       q.ksplit = best_d;
+      // Few K steps per work item: the epilogue weighs more than a deep weight ring (measured:
+      // 18-step tiles 8 % faster with the staged stores, 144-step tiles 13 % slower on 4 stages).
+      q.w_stages = iters / best_d <= 40.0 ? 4 : 5;
       const long long total = tiles * best_d;
       t->grid = dim3((unsigned)std::min<long long>(total, sms));  // persistent: one CTA per SM
       t->last_in = in;
