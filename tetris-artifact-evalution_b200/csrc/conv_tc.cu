@@ -8,12 +8,12 @@
 // the dense-contraction sub-case the design allows once a profile shows that it pays.  The
 // weights keep their zeros here; sparsity is not exploited, precision is:
 //
-//   x = x_hi + x_lo, w = w_hi + w_lo with *_hi the value rounded to TF32 and *_lo the rounded
-//   remainder; D += x_hi*w_hi + x_lo*w_hi + x_hi*w_lo in FP32 accumulators.  Rounding to
-//   nearest matters: with the truncation the tensor core applies to a raw FP32 word the
-//   per-product error (up to 3 * 2^-20) has one sign and adds up over the ~5000 products of a
-//   deep layer to more than 1e-4 of a small output; rounded, the error terms (remainder
-//   rounding and the dropped x_lo*w_lo, 2^-22 each) are symmetric and stay near 1e-6.
+//   x = x_hi + x_lo, w = w_hi + w_lo with *_hi the value rounded to TF32 (to nearest) and
+//   *_lo the remainder; D += x_hi*w_hi + x_lo*w_hi + x_hi*w_lo in FP32 accumulators.  The
+//   *_hi parts are rounded rather than left to the truncation the tensor core applies to a raw
+//   FP32 word, so that the error terms (the truncation of the remainders and the dropped
+//   x_lo*w_lo, about 2^-22 of a product each) have no preferred sign and do not add up over the
+//   ~5000 products of a deep layer.
 //
 // The tensor core adds into its FP32 accumulator with truncation, so a long accumulation chain
 // drifts toward zero (measured: 5e-5 absolute on outputs of 0.1 after the 1700 accumulation
@@ -37,7 +37,7 @@
 //   * warp 2 (one thread): one bulk copy per K step of a prepared {w_hi, w_lo} tile image into
 //     a 5-deep ring (4-deep on layers with few K steps per item, see w_stages);
 //   * warps 4-11: per K step read the patch rows of the tap (un-swizzling) and write
-//     x_hi = tf32(x) and x_lo = tf32(x - x_hi) into a 4-deep ring of 64 TMEM columns
+//     x_hi = tf32(x) and x_lo = x - x_hi into a 4-deep ring of 64 TMEM columns
 //     (tcgen05.st); warps 4-7 take the even K steps, warps 8-11 the odd ones, because one
 //     step's chain of waits, loads and stores is longer than an MMA period;
 //   * warp 3 (one thread), the gatekeeper: waits per K step for the weights, for the drained
@@ -481,9 +481,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           }
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
+            // x_hi is rounded to nearest, so the remainder's sign is random; the tensor core
+            // then truncates the (up to 13-bit) remainder itself, an error of 2^-22 |x| without
+            // a preferred sign -- rounding it here as well would cost two more operations per value
             const float v = __uint_as_float(hi[c]);
             hi[c] = round_tf32(v);
-            lo[c] = round_tf32(v - __uint_as_float(hi[c]));
+            lo[c] = __float_as_uint(v - __uint_as_float(hi[c]));
           }
           // The MMA warp waits for afull only (a wait costs it ~150 clocks in which nothing is
           // issued, and the tensor pipe holds only ~250 clocks of queued work), so afull stands
