@@ -278,3 +278,49 @@ def test_tensor_variant_random_shapes(tb, torch_cuda, oracle, seed):
     f = tb.SparseFilter(filt, ic, oc, ks)
     got = device_conv(tb, torch_cuda, f, x, stride, pad, VARIANTS["tensor"])
     check(oracle, got, oracle.host_conv2d(x, filt, stride, pad))
+
+
+def test_tensor_variant_against_list_kernel_many_shapes(tb, torch_cuda):
+    """Sixty seeded mid-size shapes (both loader modes, split K ranges, folded stems, partial
+    tiles), tensor-core variant against the list kernel on the device; then one full-size layer
+    launched ten times: a race in the tensor-core pipeline shows up as a launch that differs."""
+    torch = torch_cuda
+    rng = np.random.default_rng(2024)
+
+    def agree(ya, yb):
+        err = (ya - yb).abs()
+        return not bool((((err > 1e-4 * ya.abs()) & (err > 1e-5)) | torch.isnan(yb)).any())
+
+    for _ in range(60):
+        ks = int(rng.choice([1, 3, 3, 3, 5]))
+        stride = int(rng.choice([1, 1, 1, 2]))
+        pad = int(rng.integers(0, ks))
+        ic = int(rng.choice([3, 4, 8, 32, 64, 96, 128, 160, 256]))
+        oc = int(rng.choice([16, 64, 100, 128, 192, 256, 384]))
+        h, w = int(rng.integers(max(ks, 7), 70)), int(rng.integers(max(ks, 7), 70))
+        n = int(rng.integers(1, 20))
+        filt = rng.normal(0, 0.05, (oc, ic, ks, ks)).astype(np.float32)
+        filt[rng.random(filt.shape) < rng.choice([0.5, 0.8, 0.95])] = 0
+        f = tb.SparseFilter(filt, ic, oc, ks)
+        oh, ow = tb.out_extent(h, ks, stride, pad), tb.out_extent(w, ks, stride, pad)
+        x = torch.rand(n, h, w, ic, device="cuda") - 0.3
+        ya = torch.full((n, oh, ow, oc), float("nan"), device="cuda")
+        yb = torch.full((n, oh, ow, oc), float("nan"), device="cuda")
+        tb.sparse_conv2d(f, x, ya, n, h, w, stride, pad, variant=tb.VARIANT_TILED)
+        tb.sparse_conv2d(f, x, yb, n, h, w, stride, pad, variant=tb.VARIANT_TENSOR)
+        torch.cuda.synchronize()
+        f.check()
+        assert agree(ya, yb), dict(ks=ks, stride=stride, pad=pad, ic=ic, oc=oc, h=h, w=w, n=n)
+
+    filt = rng.normal(0, 0.05, (256, 128, 3, 3)).astype(np.float32)
+    filt[rng.random(filt.shape) < 0.85] = 0
+    f = tb.SparseFilter(filt, 128, 256, 3)
+    x = torch.rand(16, 56, 56, 128, device="cuda")
+    ref = torch.empty(16, 56, 56, 256, device="cuda")
+    tb.sparse_conv2d(f, x, ref, 16, 56, 56, 1, 1, variant=tb.VARIANT_TILED)
+    for _ in range(10):
+        y = torch.full((16, 56, 56, 256), float("nan"), device="cuda")
+        tb.sparse_conv2d(f, x, y, 16, 56, 56, 1, 1, variant=tb.VARIANT_TENSOR)
+        torch.cuda.synchronize()
+        f.check()
+        assert agree(ref, y)
