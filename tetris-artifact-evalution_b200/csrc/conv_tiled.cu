@@ -425,7 +425,9 @@ double tc_cost(const tetris_filter *f, const ConvShape &s, int sm_count) {
   const double tiles = std::ceil((double)s.N * s.OH * s.OW / 128.0 / 0.9) * ((s.OC + 127) / 128);
   // (up to 4 input channels the variant folds taps and channels into one K axis)
   const double iters = s.IC <= 4 ? (double)((s.KS * s.KS * s.IC + 31) / 32) : (double)s.KS * s.KS * ((s.IC + 31) / 32);
-  return std::ceil(tiles / sm_count) * (iters * 1500.0 + 8000.0);  // measured clocks per K step and per tile
+  // measured: ~1100 clocks per K step (conv3_3: 7 tiles x 72 steps in 0.283 ms; conv5: 144 steps in
+  // 0.088 ms) and ~3500 per tile (conv1_1 folded: 43 one-step tiles in 0.098 ms)
+  return std::ceil(tiles / sm_count) * (iters * 1100.0 + 3500.0);
 }
 
 int make_plan(const tetris_filter *f, const ConvShape &s, Plan *plan) {
