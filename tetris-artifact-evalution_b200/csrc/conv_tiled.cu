@@ -427,7 +427,7 @@ double tc_cost(const tetris_filter *f, const ConvShape &s, int sm_count) {
   const double iters = s.IC <= 4 ? (double)((s.KS * s.KS * s.IC + 31) / 32) : (double)s.KS * s.KS * ((s.IC + 31) / 32);
   // measured: ~1100 clocks per K step (conv3_3: 7 tiles x 72 steps in 0.283 ms; conv5: 144 steps in
   // 0.088 ms) and ~3500 per tile (conv1_1 folded: 43 one-step tiles in 0.098 ms)
-  return std::ceil(tiles / sm_count) * (iters * 1100.0 + 3500.0);
+  return std::ceil(tiles / sm_count) * (iters * 1050.0 + 3000.0);
 }
 
 int make_plan(const tetris_filter *f, const ConvShape &s, Plan *plan) {
@@ -436,7 +436,10 @@ int make_plan(const tetris_filter *f, const ConvShape &s, Plan *plan) {
   const int rc = enumerate_plans(f, s, &sm_count, &cands);
   if (rc) return rc;
   fill_plan(f, s, cands[0], sm_count, plan);
-  plan->use_tc = conv_tc_supported(f, s) && tc_cost(f, s, sm_count) < cands[0].cost;
+  // The list kernel's wavefront model counts issue slots only and comes out 1.2-1.75x below the
+  // measured time (1.45x on the layers where the two kernels are close); the tensor-core figure
+  // is a measured one.
+  plan->use_tc = conv_tc_supported(f, s) && tc_cost(f, s, sm_count) < 1.45 * cands[0].cost;
   return TETRIS_OK;
 }
 
