@@ -479,6 +479,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
             hi[4 * c + 0] = v.x; hi[4 * c + 1] = v.y; hi[4 * c + 2] = v.z; hi[4 * c + 3] = v.w;
           }
           }
+          // The MMA warp waits for afull only (a wait costs it ~150 clocks in which nothing is
+          // issued, and the tensor pipe holds only ~250 clocks of queued work), so afull stands
+          // for everything the MMAs of this K step need; the gatekeeper has collected the rest.
+          if (!(ok = mbar_wait_warp(bar_ready(sa), (g / kAStages) & 1, abort_flag, lane))) break;
+          // (the split comes after the wait so that the loads above are in flight during it)
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             // x_hi is rounded to nearest, so the remainder's sign is random; the tensor core
@@ -488,10 +493,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
             hi[c] = round_tf32(v);
             lo[c] = __float_as_uint(v - __uint_as_float(hi[c]));
           }
-          // The MMA warp waits for afull only (a wait costs it ~150 clocks in which nothing is
-          // issued, and the tensor pipe holds only ~250 clocks of queued work), so afull stands
-          // for everything the MMAs of this K step need; the gatekeeper has collected the rest.
-          if (!(ok = mbar_wait_warp(bar_ready(sa), (g / kAStages) & 1, abort_flag, lane))) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(kTmemA + sa * 2 * KC);
           tmem_st32(taddr, hi);
