@@ -192,6 +192,8 @@ def main():
     ap.add_argument("--no-tune", action="store_true", help="skip the untimed tile auto-tuning pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-slots", type=int, default=4, choices=[1, 2, 3, 4],
+                    help="pipeline slots (stream + workspace) the end-to-end path rotates over")
     ap.add_argument("--graph", action="store_true",
                     help="also time the step replayed as one CUDA graph (reported as `cuda_graph`)")
     args = ap.parse_args()
@@ -323,13 +325,13 @@ def main():
         hout_np = [h.numpy() for h in hout]
 
         def e2e_step():
-            # host buffers in, host buffers out; two pipeline slots, so the upload of one layer
-            # overlaps the download of the previous one; every result is on the host at the end
+            # host buffers in, host buffers out; rotating pipeline slots, so the upload of one layer
+            # overlaps the download of the previous ones; every result is on the host at the end
             for i, (h_in, h_out, l) in enumerate(zip(hin_np, hout_np, layers)):
                 L = l["L"]
-                tb.host_sync(local, i % 2)
+                tb.host_sync(local, i % args.e2e_slots)
                 tb.cuda_sparse_conv2d_async(h_in, l["f"], args.batch, L.H, L.W, L.stride, L.pad,
-                                            h_out, slot=i % 2)
+                                            h_out, slot=i % args.e2e_slots)
             tb.host_sync(local, -1)
         e2e_steps = max(1, min(args.steps, 3))
         e2e_step()
