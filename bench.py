@@ -188,7 +188,9 @@ def main():
     ap.add_argument("--oc-block", type=int, default=0, help="output channels per register block (0 = default)")
     ap.add_argument("--tile-ic", type=int, default=0, help="input channels per stage (0 = default)")
     ap.add_argument("--cudnn-context", action="store_true",
-                    help="also time cuDNN's dense FP32 convolution on the same layers (context line)")
+                    help="(kept for old command lines: the cuDNN context line is on by default at one GPU)")
+    ap.add_argument("--no-cudnn-context", action="store_true",
+                    help="skip the cuDNN dense FP32 context line")
     ap.add_argument("--no-tune", action="store_true", help="skip the untimed tile auto-tuning pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -356,7 +358,7 @@ def main():
     # ---- context line: cuDNN dense FP32 convolution (a library, not this engine) on the same
     #      shapes, as the reference does with CuDNNConv2d (Tetris/cuda_utils.cc:6-132) ----
     cudnn = None
-    if args.cudnn_context:
+    if (args.cudnn_context or world == 1) and not args.no_cudnn_context:
         import torch.nn.functional as F
         torch.backends.cudnn.benchmark = True          # cuDNN picks its fastest algorithm per shape
         torch.backends.cudnn.allow_tf32 = False        # FP32 arithmetic, like the engine
