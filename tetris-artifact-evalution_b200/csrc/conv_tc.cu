@@ -44,8 +44,8 @@
 //     partial accumulator and for the free operand stage, and passes all three on as one
 //     barrier, so that a converter warp waits once per K step and the MMA warp once;
 //   * warp 1 (converged, one elected lane issues): 12 tcgen05.mma per K step (4 K-slices x 3
-//     passes) into one of two partial accumulators in TMEM; after every second K step one
-//     tcgen05.commit releases the operand stages, and every second of those also hands the
+//     passes) into one of two partial accumulators in TMEM; after every K step one
+//     tcgen05.commit releases the operand stages, and every fourth of those also hands the
 //     partial accumulator over;
 //   * warps 12-19: read the partial accumulator (tcgen05.ld; a warp may touch the TMEM lanes
 //     of its quarter, two warps share a quarter and take half of the channels each), release
@@ -88,11 +88,13 @@ constexpr int kXBytes = 2 * kPatchBytes;     // shared memory of the activation 
 constexpr int kStoreBytes = 8 * 32 * 32 * 4;  // store staging: per summing warp 32 rows x 32 channels
 constexpr int kSmemTiles = kXBytes + kWStages * 2 * kTileBytes;  // the store staging block lies over the fifth weight stage
 static_assert(kStoreBytes <= 2 * kTileBytes, "the store staging block must fit a weight stage");
-constexpr int kPromote = 2;                 // K steps per group: one commit, releases the operand stages
-constexpr int kSuper = 2;                   // groups accumulated on the tensor core before the FP32 add outside
+constexpr int kPromote = 1;                 // K steps per group: one commit, releases the operand stages (per-step
+                                            // release measured 1-4 % faster than per two steps: the operand ring
+                                            // is only four deep)
+constexpr int kSuper = 4;                   // groups accumulated on the tensor core before the FP32 add outside
 constexpr int kTmemCols = 512;              // 2 partial accumulators (<= 128 columns each) + 4 x 64 operand columns
 constexpr int kTmemA = 256;                 // first operand column
-constexpr int kGroups = 4;                  // "group done" barriers in rotation (a group = kPromote K steps)
+constexpr int kGroups = 8;                  // "group done" barriers in rotation (a group = kPromote K steps)
 constexpr int kThreads = 640;               // warp 0 x loads, 1 MMA, 2 w loads, 4-11 convert, 12-19 sum + store
 constexpr int kNumBars = 2 * kXStages + kWStages + 2 * kAStages + kGroups + 2;
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -255,12 +257,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     h0 = (t % p.tiles_h) * p.TH;
     n0 = (t / p.tiles_h) * p.NB;
   };
-  // One tcgen05.commit per group tells everyone that the group's MMAs have completed: the
-  // summing warps take the partial accumulator, the weight loader and the converters reuse
-  // the operand stages those MMAs read.  (A commit costs the issuing thread 150-200 clocks,
-  // measured, so there is one per two K steps rather than two per K step.)  K step g of this
-  // CTA (counted across tiles) lies in group group_of(g); a stage last used by step g - depth
-  // is free once that group is done.
+  // One tcgen05.commit per group (= K step) tells everyone that the group's MMAs have
+  // completed: the weight loader and the gatekeeper reuse the operand stages those MMAs read,
+  // and after the last group of a partial sum the summing warps take the accumulator.  (A
+  // commit costs the issuing thread 150-200 clocks, measured, so there is one per K step for
+  // all purposes rather than one per ring.)  K step g of this CTA (counted across tiles) lies
+  // in group group_of(g); a stage last used by step g - depth is free once that group is done.
+  // The kGroups barriers rotate; eight are enough for every waiter to look at a group before
+  // its barrier comes round again (the MMAs are at most two partial sums ahead of the summing
+  // warps, the rings at most five K steps deep).
   auto group_of = [&](int g) { const int j = g / iters; return j * tile_groups + (g - j * iters) / kPromote; };
   auto wait_group = [&](int c) { return mbar_wait(bar_gdone(c % kGroups), (c / kGroups) & 1, abort_flag); };
   auto wait_group_warp = [&](int c) { return mbar_wait_warp(bar_gdone(c % kGroups), (c / kGroups) & 1, abort_flag, lane); };
