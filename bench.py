@@ -393,7 +393,7 @@ def main():
     per_layer = []
     for l, ms in zip(layers, layer_ms):
         L = l["L"]
-        names = {0: "tiled", 1: "generic", 2: "tiled", 3: "interp", 4: "tensor"}
+        names = {0: "tiled", 1: "generic", 2: "tiled", 4: "tensor"}
         kind = "depthwise" if L.groups != 1 else (
             "generic" if l["kernel_variant"] == 1 else
             "%s_%dx%d_s%d" % (names[l["kernel_variant"]], L.KS, L.KS, L.stride))

@@ -53,8 +53,8 @@ enum {
                                  tetris_conv2d_tune ran for it, else the cost models'      */
   TETRIS_VARIANT_GENERIC = 1, /* one thread per output pixel, any KS/stride        */
   TETRIS_VARIANT_TILED = 2,   /* shared-memory tile, per-channel weight lists          */
-  TETRIS_VARIANT_INTERP = 3,  /* shared-memory tile, jump-table interpreter that reuses a
-                                 register-resident input window across channels (1x1, 3x3) */
+                              /* 3 is retired (a jump-table interpreter kernel that measured
+                                 slower than the list kernel); it is refused as invalid      */
   TETRIS_VARIANT_TENSOR = 4   /* dense contraction on the tensor cores (tcgen05, split TF32);
                                  strides 1-8; in_channel <= 4, or a multiple of 4 with a
                                  16-byte aligned input                                    */

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtetris_b200.so")
-SOURCES = ["api.cu", "compress.cu", "conv_generic.cu", "conv_tiled.cu", "conv_interp.cu", "conv_tc.cu", "depthwise.cu", "layout.cu",
+SOURCES = ["api.cu", "compress.cu", "conv_generic.cu", "conv_tiled.cu", "conv_tc.cu", "depthwise.cu", "layout.cu",
            "noalloc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -42,9 +42,6 @@ def build(force=False, verbose=False):
     """Compile the library if it is missing or older than its sources; returns its path."""
     if not force and not needs_build():
         return LIB
-    sys.path.insert(0, CSRC)
-    import gen_interp  # the PTX interpreter cores are generated, see csrc/gen_interp.py
-    gen_interp.write()
     cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else [])
     cmd += ["-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
     res = subprocess.run(cmd, capture_output=True, text=True)

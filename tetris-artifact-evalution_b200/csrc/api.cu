@@ -74,11 +74,19 @@ int dispatch(const tetris_filter *f, const float *in, float *out, const ConvShap
   switch (variant) {
     case TETRIS_VARIANT_GENERIC: return launch_conv_generic(f, in, out, s, st);
     case TETRIS_VARIANT_TILED: return launch_conv_tiled(f, in, out, s, st, false);
-    case TETRIS_VARIANT_INTERP: return launch_conv_interp(f, in, out, s, st);
     case TETRIS_VARIANT_TENSOR: return launch_conv_tc(f, in, out, s, st);
-    case TETRIS_VARIANT_AUTO:
-      return conv_tiled_supported(f, s) ? launch_conv_tiled(f, in, out, s, st, true)
-                                        : launch_conv_generic(f, in, out, s, st);
+    case TETRIS_VARIANT_AUTO: {
+      // the list kernel (which may hand over to the tensor-core variant); when no tile geometry of
+      // it fits shared memory (long list pieces of a dense, large filter with a caller-chosen
+      // stage size) the tensor-core variant if it covers the shape, else the generic kernel
+      if (conv_tiled_supported(f, s)) {
+        const int rc = launch_conv_tiled(f, in, out, s, st, true);
+        if (rc != TETRIS_ERR_UNSUPPORTED) return rc;
+      }
+      if (conv_tc_supported(f, s) && (reinterpret_cast<uintptr_t>(in) & 15) == 0)
+        return launch_conv_tc(f, in, out, s, st);
+      return launch_conv_generic(f, in, out, s, st);
+    }
     default: set_error("unknown kernel variant %d", variant); return TETRIS_ERR_INVALID;
   }
 }
@@ -222,7 +230,7 @@ int tetris_filter_create_ex(const float *filter_oihw, int in_channel, int out_ch
   if ((rc = list_fill(d_dense, in_channel, out_channel, kernel_size, K, TIC, B, T,
                       f->d_list_offsets, f->d_lists, f->n_list_units, 0)))
     return fail(rc);
-  // ---- PROGRAM form (generic kernel, interpreter kernel) ----
+  // ---- PROGRAM form (generic kernel) ----
   if (!alloc_offsets(&f->d_prog_offsets)) {
     cudaGetLastError();
     set_error("cudaMalloc of compressor scratch failed");
@@ -416,8 +424,12 @@ int tetris_conv2d_choice(const tetris_filter_t *f, int batch_size, int img_h, in
   if (rc) return rc;
   if (!variant) { set_error("variant pointer is NULL"); return TETRIS_ERR_INVALID; }
   if (f->groups != 1) { *variant = TETRIS_VARIANT_AUTO; return TETRIS_OK; }  // depthwise: one kernel
-  if (!conv_tiled_supported(f, s)) { *variant = TETRIS_VARIANT_GENERIC; return TETRIS_OK; }
-  return conv_auto_choice(f, s, variant);
+  if (conv_tiled_supported(f, s)) {
+    rc = conv_auto_choice(f, s, variant);
+    if (rc != TETRIS_ERR_UNSUPPORTED) return rc;
+  }
+  *variant = conv_tc_supported(f, s) ? TETRIS_VARIANT_TENSOR : TETRIS_VARIANT_GENERIC;
+  return TETRIS_OK;
 }
 
 int tetris_nchw_to_nhwc(const float *d_src, float *d_dst, int N, int C, int H, int W, void *stream) {

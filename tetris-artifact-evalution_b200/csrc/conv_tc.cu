@@ -530,7 +530,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     const int quarter = warp & 3, half = (warp - 12) >> 2;
     const int row = quarter * 32 + lane;   // tile row = pixel = TMEM lane
     const int pw = row % p.TW, ph = (row / p.TW) % p.TH, pn = row / (p.TW * p.TH);
-    const bool vec = (p.OC & 3) == 0;
+    // 16-byte stores and adds need a 16-byte aligned output as well as whole groups of four channels
+    const bool vec = (p.OC & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
     const bool vec8 = (p.OC & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
     const bool small_out = (unsigned long long)p.N * p.OH * p.OW * p.OC < (1ull << 34);  // 32-bit offsets in 16-byte units
     int cbase = 0, sp = 0;  // first group of the tile; partial sum, counted across tiles

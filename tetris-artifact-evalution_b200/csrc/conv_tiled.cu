@@ -25,8 +25,9 @@
 //    loop body is load-next / FMA-current with no dependent address arithmetic.
 //
 // The kernel moves one shared-memory word per multiply-add (the same ratio as the reference,
-// see the profile summaries for what that bounds); a variant that reuses a register-resident
-// window across the K channels through a jump-table interpreter is in conv_interp.cu.
+// see the profile summaries for what that bounds).  A variant that reused a register-resident
+// window across the K channels through a jump-table interpreter (one indirect branch per weight)
+// measured 5-7 TFLOP/s against 9-12 here and was removed.
 //
 // NHWC in, NHWC out, FP32, output fully overwritten -- the contract of the reference launcher
 // (Tetris/spconv2d_kernel.cu:163-188).
@@ -253,7 +254,8 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) conv_tiled_kernel(const Tile
   if (!warp_on || !lane_on) return;
   const int oc0 = b * K;
   const int kn = min(K, p.OC - oc0);
-  const bool vec = (p.OC & 3) == 0 && kn == K;
+  // 16-byte stores need a 16-byte aligned output as well as whole groups of four channels
+  const bool vec = (p.OC & 3) == 0 && kn == K && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
 #pragma unroll
   for (int pl = 0; pl < 2; ++pl) {
     const int n = pl ? n1 : n0;

@@ -73,9 +73,6 @@ int tune_conv_tiled(const tetris_filter *f, const float *in, float *out, const C
 int conv_auto_choice(const tetris_filter *f, const ConvShape &s, int *variant);
 void *tiled_plan_cache_new();
 void tiled_plan_cache_delete(void *cache);
-bool conv_interp_supported(const tetris_filter *f, const ConvShape &s);
-int launch_conv_interp(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
-                       cudaStream_t st);
 int conv_tc_prepare(tetris_filter *f, const float *d_dense);
 void conv_tc_state_delete(void *state);
 bool conv_tc_supported(const tetris_filter *f, const ConvShape &s);
