@@ -25,6 +25,9 @@
  *   tetris_nchw_to_nhwc/
  *   tetris_nhwc_to_nchw       NCHW2NHWC / NHWC2NCHW, Tetris/tensor_utils.cc:85-111,
  *                             done on the device
+ *   tetris_filter_save/_load  no counterpart as calls: they replace REPEATING the constructor's
+ *                             compress + upload (Tetris/spconv2d_utils.h:248-264) per process
+ *                             and per timed tile configuration (Tetris/spconv2d.cc:285-311)
  *   tetris_conv2d_host_sharded  no counterpart (the reference pins device 0,
  *                             Tetris/spconv2d.cc:379-380): batch slices of one
  *                             call run on several GPUs of one box
@@ -66,7 +69,8 @@ typedef struct tetris_filter tetris_filter_t; /* opaque; owns device buffers */
 typedef struct {
   int oc_block;  /* output channels per register block, 8 (default) or 16            */
   int tile_ic;   /* input channels per stage, multiple of 4, <= 64                 */
-  int reserved[6];
+  int deterministic; /* 1: bit-reproducible results from launch to launch (see tetris_conv2d_launch) */
+  int reserved[5];
 } tetris_filter_opts_t;
 
 typedef struct {
@@ -120,6 +124,15 @@ int tetris_filter_check(const tetris_filter_t *f);
  * Convolution, device pointers, NHWC in and NHWC out as in the reference
  * launcher; asynchronous on `stream` (a cudaStream_t, may be NULL); allocates
  * nothing; the output is fully overwritten.  The device of `f` must be current.
+ * Pointers need 4-byte alignment only; 16-byte aligned tensors take the vector paths (the
+ * tensor-core variant needs a 16-byte aligned input and is not chosen without one).
+ * Reproducibility: the list, generic and depthwise kernels add each output's taps in a fixed
+ * order.  The tensor-core variant, on layers whose tiles fill the last wave of SMs badly, cuts
+ * every tile's K range into 2-8 work items that ADD their partial results into the zeroed output
+ * with floating-point atomics, in whatever order they finish: such a launch is not bit-identical
+ * from run to run (differences of a few 1e-7 relative).  A filter created with
+ * tetris_filter_opts_t.deterministic = 1 never splits and is bit-reproducible, at the cost of
+ * the badly filled wave.
  */
 int tetris_conv2d_launch(const tetris_filter_t *f, const float *d_input_nhwc,
                          float *d_output_nhwc, int batch_size, int img_h, int img_w,
@@ -222,7 +235,10 @@ int tetris_device_info(int device, int *sm_count, int *sm_clock_khz, int *fp32_l
  *    more pieces than that are refused with TETRIS_ERR_UNSUPPORTED and a message.  Every GPU that
  *    loads the library holds that array until the process exits.
  *  - The first call on a device looks up the array's device address (once per device, that
- *    device being current); make that first call before any stream capture begins.
+ *    device being current) and, where the CUDA runtime loads code lazily, may load the library's
+ *    kernels; make that first call at start-up, before any stream capture begins.
+ *  - Both pointers are checked to be device memory of the current device (TETRIS_ERR_INVALID
+ *    otherwise); the check is a query and allocates nothing.
  *  - All calls share the array, so two calls that can overlap on the GPU (different streams, or
  *    different host threads) race on it; keep calls on one device in stream order.  Nothing has
  *    to be cleared between calls: each call rewrites every count it later reads.
@@ -230,6 +246,33 @@ int tetris_device_info(int device, int *sm_count, int *sm_clock_khz, int *fp32_l
 int tetris_list_offsets_noalloc(const float *d_filter_oihw, int in_channel, int out_channel,
                                 int kernel_size, int oc_block, int tile_ic,
                                 int32_t *d_list_offsets, void *stream);
+
+/*
+ * Compressed-filter files.  The reference recompresses every filter in every process and once
+ * per tile configuration it times (upload at Tetris/spconv2d_utils.h:248-264, rebuild loop at
+ * Tetris/spconv2d.cc:285-311); these three calls make that a one-off.
+ *   tetris_filter_save        writes both compressed forms as they lie on the device (for a
+ *                             depthwise filter its dense taps) and the tile plans
+ *                             tetris_conv2d_tune has chosen so far, behind a versioned header
+ *                             with a checksum.
+ *   tetris_filter_load        reads such a file onto `device`: same downloads, same launches and
+ *                             the same tuned choices as the filter that was saved.  The
+ *                             tensor-core tile images are rebuilt on the device from the list form.
+ *   tetris_filter_file_check  validates a file on the host alone (no GPU): header, sizes,
+ *                             offsets, checksum; fills `info` (may be NULL; info->device = -1).
+ * A missing, truncated, foreign or damaged file is TETRIS_ERR_INVALID with the reason in
+ * tetris_last_error().
+ */
+int tetris_filter_save(const tetris_filter_t *f, const char *path);
+int tetris_filter_load(const char *path, int device, tetris_filter_t **out);
+int tetris_filter_file_check(const char *path, tetris_filter_info_t *info);
+
+/*
+ * Number of convolution kernels the library has launched in this process so far (every variant,
+ * every device and thread; tuning launches included).  No counterpart in the reference; lets a
+ * harness check that a timing loop really issued warm + repeat launches.
+ */
+unsigned long long tetris_launch_count(void);
 
 /* Text of the last error raised on this thread ("" if none). */
 const char *tetris_last_error(void);

@@ -18,9 +18,15 @@ _I, _VP = ctypes.c_int, ctypes.c_void_p
 _port = _ref = None
 
 
-def build(ref_root="/root/reference"):
+def reference_root():
+    """Where the reference checkout lies: $TETRIS_REFERENCE_ROOT, else a directory named
+    `reference` beside this repository."""
+    return os.environ.get("TETRIS_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
+def build(ref_root=None):
     """Run the Makefile: always the port; the compiled reference when its sources are there."""
-    subprocess.run(["make", "-s", "-C", _HERE, "REF=" + ref_root, "all"], check=True)
+    subprocess.run(["make", "-s", "-C", _HERE, "REF=" + (ref_root or reference_root()), "all"], check=True)
 
 
 def port():

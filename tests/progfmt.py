@@ -123,3 +123,48 @@ def unpack_lists(units, offsets, OC, IC, KS, K=16, TIC=16):
                     w[b * K + k, t * TIC + (pos >> 8), (pos >> 4) & 15, pos & 15] = val
             assert words[i] == 0 and words[i + 1] == TIC << 8  # the sentinels
     return w.view(np.float32)
+
+
+# ---- compressed-filter files (tetris_filter_save / _load / _file_check) ----------------------
+FILE_MAGIC = b"TETRISF1"
+FILE_VERSION = 1
+FILE_HEADER = "<8sII" + "i" * 12 + "qqq" + "QQ"   # see FileHeader in csrc/serialize.cu
+TUNED_INTS = 9
+
+
+def fnv1a(data):
+    h = 1469598103934665603
+    for byte in data:
+        h = ((h ^ byte) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    return h
+
+
+def write_filter_file(path, w, K=8, TIC=16, tuned=(), damage=None):
+    """Checker-side writer of the file format: what tetris_filter_save must produce for the dense
+    OIHW filter `w` (groups == 1).  `damage(header_fields, payload) -> (header_fields, payload)`
+    lets a test corrupt the file before it is written."""
+    import struct
+    w = np.ascontiguousarray(w, np.float32)
+    OC, IC, KS, _ = w.shape
+    B, T = -(-OC // K), -(-IC // TIC)
+    ops, poffs, nnz = pack(w, K, TIC)
+    units, loffs = pack_lists(w, K, TIC)
+    tuned = np.asarray(tuned, np.int32).reshape(-1, TUNED_INTS)
+    payload = loffs.tobytes() + poffs.tobytes() + units.tobytes() + ops.tobytes() + tuned.tobytes()
+    fields = dict(in_channel=IC, out_channel=OC, kernel_size=KS, groups=1, oc_block=K, tile_ic=TIC,
+                  n_oc_blocks=B, n_stages=T, max_prog_ops=int(np.diff(poffs).max()),
+                  max_list_units=int(np.diff(loffs).max()), deterministic=0, n_tuned=len(tuned),
+                  nnz=nnz, n_ops=ops.size, n_list_units=units.size)
+    if damage:
+        fields, payload = damage(fields, payload)
+    fields.setdefault("payload_bytes", len(payload))
+    fields.setdefault("checksum", fnv1a(payload))
+    header = struct.pack(FILE_HEADER, fields.get("magic", FILE_MAGIC), fields.get("version", FILE_VERSION),
+                         struct.calcsize(FILE_HEADER),
+                         *[fields[k] for k in ("in_channel", "out_channel", "kernel_size", "groups", "oc_block",
+                                               "tile_ic", "n_oc_blocks", "n_stages", "max_prog_ops",
+                                               "max_list_units", "deterministic", "n_tuned", "nnz", "n_ops",
+                                               "n_list_units", "payload_bytes", "checksum")])
+    with open(path, "wb") as fh:
+        fh.write(header + payload)
+    return header, payload

@@ -211,8 +211,14 @@ def test_timing_harness_runs(tb, torch_cuda):
     f = tb.SparseFilter(filt, 64, 64, 3)
     x = torch_cuda.rand(1, 56, 56, 64, device="cuda")
     y = torch_cuda.empty(1, 56, 56, 64, device="cuda")
+    torch_cuda.cuda.synchronize()
+    before = tb.launch_count()
     ms = tb.timing_sparse_conv2d(f, x, y, 1, 56, 56, 1, 1, warm=3, repeat=10)
     assert 0.0 < ms < 50.0
+    assert tb.launch_count() - before == 3 + 10   # warm + repeat launches, as the protocol says
+    before = tb.launch_count()
+    tb.timing_sparse_conv2d(f, x, y, 1, 56, 56, 1, 1)
+    assert tb.launch_count() - before == tb.WARM + tb.REPEAT == 130
 
 
 def test_tile_tuning_keeps_results_and_reports_a_time(tb, torch_cuda, oracle):

@@ -43,6 +43,38 @@ def test_two_calls_in_a_row_match_the_allocating_path(tb, torch_cuda):
         assert np.array_equal(d_out.cpu().numpy(), want)
 
 
+def test_device_memory_is_untouched_and_the_limit_itself_is_accepted(tb, torch_cuda):
+    """The point of the entry point: a call changes nothing in the device's free memory.  And a
+    filter with exactly as many pieces as the scratch array holds (128 channel blocks x 128
+    stages = 16384) is served, with the same offsets as the allocating path."""
+    torch = torch_cuda
+    rng = np.random.default_rng(5)
+    w = rng.normal(0, 0.05, (1024, 512, 1, 1)).astype(np.float32)
+    w[rng.random(w.shape) < 0.9] = 0
+    want = reference_offsets(tb, w, 8, 4)
+    assert want.size == 16384 + 1
+    d_w = torch.from_numpy(w).cuda()
+    d_out = torch.full((want.size,), -1, dtype=torch.int32, device="cuda")
+    tb.list_offsets_noalloc(d_w, 512, 1024, 1, 8, 4, d_out)  # warm-up: symbol lookup, module load
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    d_out.fill_(-1)
+    tb.list_offsets_noalloc(d_w, 512, 1024, 1, 8, 4, d_out)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert np.array_equal(d_out.cpu().numpy(), want)
+
+
+def test_host_pointers_are_refused(tb, torch_cuda):
+    torch = torch_cuda
+    host = np.zeros((16, 16), np.float32)
+    out = torch.zeros(8, dtype=torch.int32, device="cuda")
+    with pytest.raises(tb.TetrisError) as e:
+        tb.list_offsets_noalloc(host, 16, 16, 1, 8, 4, out)
+    assert e.value.status == 1 and "device memory" in str(e.value)
+
+
 def test_sizes_beyond_the_scratch_are_refused(tb, torch_cuda):
     torch = torch_cuda
     d = torch.zeros(16, device="cuda")

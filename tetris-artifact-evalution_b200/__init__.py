@@ -38,7 +38,8 @@ _c_int_p = ctypes.POINTER(ctypes.c_int)
 
 
 class FilterOpts(ctypes.Structure):
-    _fields_ = [("oc_block", ctypes.c_int), ("tile_ic", ctypes.c_int), ("reserved", ctypes.c_int * 6)]
+    _fields_ = [("oc_block", ctypes.c_int), ("tile_ic", ctypes.c_int), ("deterministic", ctypes.c_int),
+                ("reserved", ctypes.c_int * 5)]
 
 
 class FilterInfo(ctypes.Structure):
@@ -79,6 +80,10 @@ SIGNATURES = {
     "tetris_batch_slice": (_I, [_I, _I, _I, _c_int_p, _c_int_p]),
     "tetris_device_info": (_I, [_I, _c_int_p, _c_int_p, _c_int_p]),
     "tetris_list_offsets_noalloc": (_I, [_VP, _I, _I, _I, _I, _I, _VP, _VP]),
+    "tetris_filter_save": (_I, [_VP, ctypes.c_char_p]),
+    "tetris_filter_load": (_I, [ctypes.c_char_p, _I, ctypes.POINTER(_VP)]),
+    "tetris_filter_file_check": (_I, [ctypes.c_char_p, ctypes.POINTER(FilterInfo)]),
+    "tetris_launch_count": (ctypes.c_ulonglong, []),
     "tetris_last_error": (ctypes.c_char_p, []),
 }
 
@@ -151,23 +156,40 @@ class SparseFilter:
     """
 
     def __init__(self, filter, in_channel, out_channel, kernel_size, TILE_IC=0,
-                 apply_reorder=True, apply_vectorize=True, groups=1, device=0, oc_block=0):
+                 apply_reorder=True, apply_vectorize=True, groups=1, device=0, oc_block=0,
+                 deterministic=False):
         per_oc = 1 if groups != 1 else in_channel
         dense = np.ascontiguousarray(filter, dtype=np.float32).reshape(-1)
         expect = out_channel * per_oc * kernel_size * kernel_size
         if dense.size != expect:
             raise ValueError("filter has %d elements, expected %d" % (dense.size, expect))
         self._handle = _VP()
-        opts = FilterOpts(oc_block=oc_block, tile_ic=TILE_IC)
+        opts = FilterOpts(oc_block=oc_block, tile_ic=TILE_IC, deterministic=1 if deterministic else 0)
         _check(lib().tetris_filter_create_ex(dense.ctypes.data, in_channel, out_channel, kernel_size,
                                              groups, device, ctypes.byref(opts),
                                              ctypes.byref(self._handle)))
+        self._adopt(device)
+
+    def _adopt(self, device):
         info = self.info()
-        self.in_channel_, self.out_channel_, self.kernel_size_ = in_channel, out_channel, kernel_size
-        self.groups_ = groups
+        self.in_channel_, self.out_channel_, self.kernel_size_ = info.in_channel, info.out_channel, info.kernel_size
+        self.groups_ = info.groups
         self.nnz_ = info.nnz
         self.TILE_IC_ = info.tile_ic
         self.device_ = device
+
+    def save(self, path):
+        """Write the compressed forms and the tuned tile plans to `path` (tetris_filter_save)."""
+        _check(lib().tetris_filter_save(self.handle, os.fsencode(path)))
+
+    @classmethod
+    def load(cls, path, device=0):
+        """A filter read back from a file written by save(): no recompression, same tuned plans."""
+        self = cls.__new__(cls)
+        self._handle = _VP()
+        _check(lib().tetris_filter_load(os.fsencode(path), device, ctypes.byref(self._handle)))
+        self._adopt(device)
+        return self
 
     def info(self):
         info = FilterInfo()
@@ -315,6 +337,18 @@ def nchw_to_nhwc(src, dst, N, C, H, W, cuda_stream=None):
 
 def nhwc_to_nchw(src, dst, N, C, H, W, cuda_stream=None):
     _check(lib().tetris_nhwc_to_nchw(_ptr(src), _ptr(dst), N, C, H, W, _stream_ptr(cuda_stream)))
+
+
+def filter_file_check(path):
+    """Validate a compressed-filter file on the host alone; returns its FilterInfo."""
+    info = FilterInfo()
+    _check(lib().tetris_filter_file_check(os.fsencode(path), ctypes.byref(info)))
+    return info
+
+
+def launch_count():
+    """Convolution kernels launched through the library by this process so far."""
+    return int(lib().tetris_launch_count())
 
 
 def batch_slice(batch_size, world, rank):

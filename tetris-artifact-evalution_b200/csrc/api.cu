@@ -4,6 +4,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 #include <new>
 #include <string>
@@ -15,6 +16,9 @@
 namespace tetris {
 
 static thread_local char g_error[512] = "";
+static std::atomic<unsigned long long> g_launches{0};
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 void set_error(const char *fmt, ...) {
   va_list ap;
@@ -100,6 +104,8 @@ extern "C" {
 
 const char *tetris_last_error(void) { return g_error; }
 
+unsigned long long tetris_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
 int tetris_filter_create(const float *filter_oihw, int in_channel, int out_channel,
                          int kernel_size, int groups, int device, tetris_filter_t **out) {
   return tetris_filter_create_ex(filter_oihw, in_channel, out_channel, kernel_size, groups, device,
@@ -146,6 +152,7 @@ int tetris_filter_create_ex(const float *filter_oihw, int in_channel, int out_ch
   f->in_channel = in_channel; f->out_channel = out_channel; f->kernel_size = kernel_size;
   f->groups = groups; f->device = device;
   f->oc_block = K; f->tile_ic = TIC;
+  f->deterministic = opts && opts->deterministic ? 1 : 0;
   f->plan_cache = tiled_plan_cache_new();
 
   const size_t per_oc = depthwise ? 1 : (size_t)in_channel;

@@ -61,6 +61,7 @@ int launch_conv_generic(const tetris_filter *f, const float *in, float *out, con
                                             f->d_prog_offsets, s, f->oc_block, f->tile_ic,
                                             f->n_stages);
   TETRIS_CUDA_TRY(cudaGetLastError());
+  count_launch();
   return TETRIS_OK;
 }
 

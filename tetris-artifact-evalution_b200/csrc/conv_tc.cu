@@ -729,13 +729,21 @@ struct TcState {
   int *d_error = nullptr;
   int n_chunks = 0, bn = 128;  // K chunks per tap; channel tile (fixed by the filter: 64 up to 64 channels)
   bool folded = false;         // <= 4 input channels: taps and channels folded into one K axis
-  // activation map of the last input pointer / shape
+  // Launch set-ups (tensor map of the input, tile plan, grid), one per (input pointer, conv
+  // shape) seen lately: a caller that rotates over a few buffers -- the pipelined host path has
+  // four -- finds its map again instead of encoding one per launch.  Round-robin replacement.
+  struct Setup {
+    bool valid = false;
+    const float *in = nullptr;
+    ConvShape shape{};
+    CUtensorMap map_x;
+    TcParams params{};
+    dim3 grid;
+  };
+  static constexpr int kSetups = 8;
   std::mutex mutex;
-  const float *last_in = nullptr;
-  ConvShape last_shape{};
-  CUtensorMap map_x;
-  TcParams params{};
-  dim3 grid;
+  Setup setups[kSetups];
+  int next_setup = 0;
 };
 
 }  // namespace
@@ -795,9 +803,15 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
   int bn = 128;
   {
     std::lock_guard<std::mutex> lock(t->mutex);
-    const ConvShape &l = t->last_shape;
-    const bool hit = t->last_in == in && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S;
-    if (!hit) {
+    TcState::Setup *su = nullptr;
+    for (TcState::Setup &c : t->setups) {
+      const ConvShape &l = c.shape;
+      if (c.valid && c.in == in && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S) { su = &c; break; }
+    }
+    if (!su) {
+      su = &t->setups[t->next_setup];
+      t->next_setup = (t->next_setup + 1) % TcState::kSetups;
+      su->valid = false;
       // pixels of a tile: TW x TH x NB rows, at most 128, as full as possible, and -- at stride
       // 1, where all taps read one patch -- such that the tile with its halo fits a stage
       // (1x1 filters have no halo to share either, and the per-K-step ring is four deep)
@@ -826,10 +840,10 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
       const cuuint32_t box[4] = {KC, (cuuint32_t)(PW * s.S), (cuuint32_t)(PH * s.S), (cuuint32_t)best_nb};
       const cuuint32_t estr[4] = {1, (cuuint32_t)s.S, (cuuint32_t)s.S, 1};
       if (!t->folded) {  // (folded mode reads the activations with plain loads)
-        const int rc = encode_map(&t->map_x, const_cast<float *>(in), 4, dims, strides, box, estr);
+        const int rc = encode_map(&su->map_x, const_cast<float *>(in), 4, dims, strides, box, estr);
         if (rc) return rc;
       }
-      TcParams &q = t->params;
+      TcParams &q = su->params;
       q.N = s.N; q.OH = s.OH; q.OW = s.OW; q.OC = s.OC; q.P = s.P; q.KS = s.KS;
       q.TW = best_tw; q.TH = best_th; q.NB = best_nb;
       q.PW = PW; q.PH = PH;
@@ -854,7 +868,7 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
       const double zeroing = ((double)s.N * s.OH * s.OW * s.OC * 4 / 6.0e12 + 3e-6) * 1.9e9 / 1450.0;
       int best_d = 1;
       double best_cost = std::ceil((double)tiles / sms) * (iters + 10.0);
-      for (int d = 2; d <= 8 && d <= q.n_chunks; ++d) {
+      for (int d = 2; d <= 8 && d <= q.n_chunks && !f->deterministic; ++d) {
         if (q.n_chunks % d) continue;
         const double cost = std::ceil((double)tiles * d / sms) * (iters / d + 10.0) + zeroing;
         if (cost < 0.96 * best_cost) { best_cost = cost; best_d = d; }
@@ -864,16 +878,18 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
       // 18-step tiles 8 % faster with the staged stores, 144-step tiles 13 % slower on 4 stages).
       q.w_stages = iters / best_d <= 40.0 ? 4 : 5;
       const long long total = tiles * best_d;
-      t->grid = dim3((unsigned)std::min<long long>(total, sms));  // persistent: one CTA per SM
-      t->last_in = in;
-      t->last_shape = s;
+      su->grid = dim3((unsigned)std::min<long long>(total, sms));  // persistent: one CTA per SM
+      su->in = in;
+      su->shape = s;
+      su->valid = true;
     }
-    map_x = t->map_x;
-    p = t->params;
-    grid = t->grid;
+    map_x = su->map_x;
+    p = su->params;
+    grid = su->grid;
     bn = t->bn;
   }
   p.out = out;
+  p.in = in;
   const size_t smem = (size_t)kSmemTiles + 1024 + kNumBars * 8 + 16;
   static thread_local bool configured[16] = {false};
   int dev = 0;
@@ -890,6 +906,7 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
   else
     conv_tc_kernel<128><<<grid, kThreads, smem, st>>>(map_x, p);
   TETRIS_CUDA_TRY(cudaGetLastError());
+  count_launch();
   return TETRIS_OK;
 }
 

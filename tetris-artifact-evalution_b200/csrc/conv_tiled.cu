@@ -461,6 +461,7 @@ int launch_instance(const Plan &plan, const float *in, float *out, cudaStream_t 
   p.out = out;
   kern<<<plan.grid, WARPS * 32, plan.smem_bytes, st>>>(p);
   TETRIS_CUDA_TRY(cudaGetLastError());
+  count_launch();
   return TETRIS_OK;
 }
 
@@ -479,6 +480,47 @@ bool same_shape(const ConvShape &a, const ConvShape &b) {
 
 void *tiled_plan_cache_new() { return new (std::nothrow) PlanCache(); }
 void tiled_plan_cache_delete(void *c) { delete static_cast<PlanCache *>(c); }
+
+void tiled_plans_export(const tetris_filter *f, std::vector<int32_t> *out) {
+  PlanCache *cache = static_cast<PlanCache *>(f->plan_cache);
+  if (!cache) return;
+  std::lock_guard<std::mutex> lock(cache->mutex);
+  for (const Plan &t : cache->tuned) {
+    const int32_t rec[kTunedInts] = {t.shape.N, t.shape.H, t.shape.W, t.shape.S, t.shape.P,
+                                     t.instance, t.p.NSEG, t.p.TH, t.use_tc ? 1 : 0};
+    out->insert(out->end(), rec, rec + kTunedInts);
+  }
+}
+
+// Rebuilds each plan from its tile shape; records that do not fit this filter any more (another
+// device with less shared memory, a damaged record) are skipped: the launch then plans afresh.
+void tiled_plans_import(const tetris_filter *f, const int32_t *plans, int n) {
+  PlanCache *cache = static_cast<PlanCache *>(f->plan_cache);
+  if (!cache || f->groups != 1) return;
+  int dev = 0, sm_count = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return;
+  for (int i = 0; i < n; ++i) {
+    const int32_t *r = plans + (size_t)i * kTunedInts;
+    ConvShape s;
+    s.N = r[0]; s.H = r[1]; s.W = r[2]; s.S = r[3]; s.P = r[4];
+    s.IC = f->in_channel; s.OC = f->out_channel; s.KS = f->kernel_size;
+    if (s.N < 1 || s.H < 1 || s.W < 1 || s.S < 1 || s.P < 0 || s.H + 2 * s.P < s.KS || s.W + 2 * s.P < s.KS) continue;
+    s.OH = (s.H + 2 * s.P - s.KS) / s.S + 1;
+    s.OW = (s.W + 2 * s.P - s.KS) / s.S + 1;
+    const int inst = r[5], NSEG = r[6], TH = r[7];
+    if (!conv_tiled_supported(f, s) || inst < 0 || inst >= (int)(sizeof(kInstances) / sizeof(kInstances[0])) ||
+        kInstances[inst].K != f->oc_block || NSEG < 1 || TH < 1 || NSEG * TH > 32)
+      continue;
+    Plan plan;
+    if (plan_cost(f, s, kInstances[inst], NSEG, TH, sm_count, kSmemLimit, &plan) < 0.0) continue;
+    plan.instance = inst;
+    plan.use_tc = r[8] != 0 && conv_tc_supported(f, s);
+    std::lock_guard<std::mutex> lock(cache->mutex);
+    if (cache->tuned.size() < 8) cache->tuned.push_back(plan);
+  }
+}
 
 bool conv_tiled_supported(const tetris_filter *f, const ConvShape &s) {
   if (f->groups != 1 || !f->d_lists) return false;

@@ -123,6 +123,7 @@ int launch_depthwise(const tetris_filter *f, const float *in, float *out, const 
     depthwise_any_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, st>>>(in, out, f->d_dense, s);
   }
   TETRIS_CUDA_TRY(cudaGetLastError());
+  count_launch();
   return TETRIS_OK;
 }
 

@@ -5,6 +5,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <vector>
+
 #include "../../include/tetris_b200.h"
 #include "format.h"
 
@@ -23,6 +25,7 @@ struct tetris_filter {
   int32_t *d_list_offsets; // n_oc_blocks * n_stages + 1 unit indices
   int64_t n_list_units;
   int max_list_units;      // longest piece, in 8-byte units
+  int deterministic;       // 1: the tensor-core variant never splits a tile's K range (no atomic adds)
   void *plan_cache;        // tiled kernel: launch plan of the last conv shape (conv_tiled.cu)
   void *tc_state;          // tensor-core variant: split dense weights + tensor maps (conv_tc.cu)
 };
@@ -72,6 +75,13 @@ int tune_conv_tiled(const tetris_filter *f, const float *in, float *out, const C
                     cudaStream_t st, int max_candidates, float *best_ms);
 int conv_auto_choice(const tetris_filter *f, const ConvShape &s, int *variant);
 void *tiled_plan_cache_new();
+// The plans tetris_conv2d_tune chose, as kTunedInts ints each: the conv shape (N, H, W, S, P),
+// the kernel instance, the tile shape (NSEG, TH) and whether the tensor-core variant won.
+constexpr int kTunedInts = 9;
+void tiled_plans_export(const tetris_filter *f, std::vector<int32_t> *out);
+void tiled_plans_import(const tetris_filter *f, const int32_t *plans, int n);
+// conv kernel launches issued through the library by this process (all devices, all threads)
+void count_launch();
 void tiled_plan_cache_delete(void *cache);
 int conv_tc_prepare(tetris_filter *f, const float *d_dense);
 void conv_tc_state_delete(void *state);

@@ -73,6 +73,23 @@ extern "C" int tetris_list_offsets_noalloc(const float *d_filter_oihw, int in_ch
               pieces, B, T, kNoAllocMaxPieces);
     return TETRIS_ERR_UNSUPPORTED;
   }
+  // Both arrays have to be device memory of the CURRENT device: the scratch array used below is
+  // the current device's copy, and a host pointer handed to the kernels would fault.  (A query,
+  // not an allocation.)
+  int dev = -1;
+  TETRIS_CUDA_TRY(cudaGetDevice(&dev));
+  const void *ptrs[2] = {d_filter_oihw, d_list_offsets};
+  for (const void *ptr : ptrs) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess ||
+        !(attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) ||
+        (attr.type == cudaMemoryTypeDevice && attr.device != dev)) {
+      cudaGetLastError();
+      set_error("the %s is not device memory of the current device %d",
+                ptr == d_filter_oihw ? "filter" : "offsets array", dev);
+      return TETRIS_ERR_INVALID;
+    }
+  }
   int32_t *d_counts = nullptr;
   int rc = scratch_for_current_device(&d_counts);
   if (rc) return rc;

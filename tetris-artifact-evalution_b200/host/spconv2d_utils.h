@@ -31,9 +31,14 @@ struct SparseFilter {
     (void)apply_vectorize;  // ... and always streams them with vector loads
     int device = 0;
     checkCudaErrors(cudaGetDevice(&device));
-    // TILE_IC of the reference is a tile-table entry chosen per timed candidate; the engine picks
-    // its stage size from the kernel size and sparsity, so the argument is not forwarded.
-    checkTetris(tetris_filter_create(filter, in_channel, out_channel, kernel_size, 1, device, &handle_));
+    // TILE_IC of the reference is a tile-table entry chosen per timed candidate
+    // (Tetris/spconv2d.cc:90-275).  Its default argument, 32, selects the engine's own stage
+    // size (chosen from the kernel size and the longest list piece); any other value the engine
+    // accepts as a stage size (4, 8, 16, 64) is forwarded; a value it cannot use (e.g. 24) also
+    // falls back to the engine's choice, and GetTileIC() / TILE_IC_ report what was used.
+    tetris_filter_opts_t opts = {};
+    if (TILE_IC != 32 && TILE_IC >= 4 && TILE_IC <= 64 && (TILE_IC & (TILE_IC - 1)) == 0) opts.tile_ic = TILE_IC;
+    checkTetris(tetris_filter_create_ex(filter, in_channel, out_channel, kernel_size, 1, device, &opts, &handle_));
     tetris_filter_info_t info;
     checkTetris(tetris_filter_info(handle_, &info));
     nnz_ = (int)info.nnz;
@@ -57,6 +62,14 @@ struct SparseFilter {
   int nnz_;
   int TILE_IC_;
   std::vector<OffsetType> oc_permutation_;
+  // The reference keeps host copies of its device arrays in these four public fields
+  // (Tetris/spconv2d_utils.h:505-514).  The engine compresses on the device into a layout of
+  // its own, so they stay EMPTY here; tetris_filter_download / tetris_filter_download_lists
+  // return the engine's forms for a host that wants to look at them.
+  std::vector<OffsetType> stage_len_;
+  std::vector<OffsetType> offsets_;
+  std::vector<PositionType> position_;
+  std::vector<ValueType> values_;
 
  private:
   tetris_filter_t *handle_;
