@@ -6,6 +6,8 @@ generated: weights ~ N(0, 0.05) with an exact-count uniform-random zero mask, ac
 uniform[0, 1) with an independent Bernoulli(0.5) zero mask.  Every tensor is a pure function
 of (workload name, layer index, kind), so the CPU oracle and the GPU path see identical data.
 """
+import glob
+import os
 import zlib
 from collections import namedtuple
 
@@ -100,12 +102,56 @@ def yolov3(size=416):
     return layers
 
 
+# ---- real pruned layers -----------------------------------------------------------------------
+# Compact copies (shape + indices and values of the nonzero weights) of layer dumps of pruned
+# checkpoints in the reference's text format (header `H W IC OC KS Pad S G`, then the OIHW
+# floats, Tetris/tensor_utils.cc:55-82).  Magnitude pruning leaves very uneven rows, rows with no
+# nonzeros and |w| up to ~2 -- unlike the uniform masks above.  The directory is
+# $TETRIS_REAL_LAYERS, else tests/real_layers beside the package.
+def real_layer_dir():
+    here = os.path.dirname(os.path.abspath(__file__))
+    return os.environ.get("TETRIS_REAL_LAYERS") or os.path.join(os.path.dirname(here), "tests", "real_layers")
+
+
+def real_layer_files():
+    return sorted(glob.glob(os.path.join(real_layer_dir(), "*.npz")))
+
+
+def load_real_layer(path):
+    """(Layer, dense OIHW float32 filter) of one compact layer file."""
+    z = np.load(path)
+    h, w, ic, oc, ks, pad, stride, groups = (int(v) for v in z["header"])
+    dense = np.zeros(oc * ic * ks * ks, np.float32)
+    dense[z["index"]] = z["value"]
+    name = os.path.basename(path)[:-4]
+    short = name.split("__")[0] + "_" + "_".join(name.split("_H_")[1].split("_")[i] for i in (0, 3, 5, 7, 11))
+    sparsity = 1.0 - z["index"].size / dense.size
+    # the reference reads the groups field and ignores it (Tetris/tensor_utils.cc:66)
+    return Layer(short, h, w, ic, oc, ks, pad, stride, 1, sparsity), dense.reshape(oc, ic, ks, ks)
+
+
+def real_layers():
+    return [load_real_layer(p)[0] for p in real_layer_files()]
+
+
+def uniform_like(filt, seed=0):
+    """A filter of the same shape and nonzero count (and the same nonzero values) whose nonzeros
+    sit at uniformly random positions: the uniform-mask twin of a pruned layer."""
+    rng = np.random.Generator(np.random.Philox(key=seed))
+    flat = filt.reshape(-1)
+    vals = flat[flat != 0]
+    out = np.zeros_like(flat)
+    out[rng.permutation(flat.size)[:vals.size]] = vals
+    return out.reshape(filt.shape)
+
+
 WORKLOADS = {
     "single": single_layer,
     "vgg19": vgg19,
     "resnet50": resnet50,
     "mobilenet": mobilenet_v1,
     "yolov3": yolov3,
+    "real": real_layers,
 }
 
 
@@ -123,6 +169,8 @@ def layer_sparsity(workload, layer_idx, layer):
 
 def make_filter(workload, layer_idx, layer):
     """Dense OIHW float32 filter ([C][1][KS][KS] for depthwise) with an exact-count zero mask."""
+    if workload == "real":
+        return load_real_layer(real_layer_files()[layer_idx])[1]
     per_oc = 1 if layer.groups != 1 else layer.IC
     shape = (layer.OC, per_oc, layer.KS, layer.KS)
     rng = _rng(workload, layer_idx, "filter")
