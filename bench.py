@@ -39,8 +39,11 @@ NCU_TRAFFIC = {
                      "note": "captured on VGG-19 conv2_2 batch 16: 270.5 MB per launch against 205.7 MB "
                              "algorithmic; scaled by algorithmic bytes"},
 }
-VARIANT_NAMES = {0: "auto", 1: "generic", 2: "tiled", 4: "tensor"}
-ARITH = {"tensor": "3xTF32 split on the tensor cores (x_hi*w_hi + x_lo*w_hi + x_hi*w_lo), FP32 accumulate, "
+VARIANT_NAMES = {0: "auto", 1: "generic", 2: "tiled", 4: "tensor", 5: "tensor16"}
+ARITH = {"tensor16": "3xFP16 split on the tensor cores (x_hi*w_hi + x_lo*w_hi + x_hi*w_lo, 11-bit halves), FP32 "
+                     "accumulate, partial sums added on the CUDA cores every 48 MMAs; out-of-range activations "
+                     "recomputed in 3xTF32",
+         "tensor": "3xTF32 split on the tensor cores (x_hi*w_hi + x_lo*w_hi + x_hi*w_lo), FP32 accumulate, "
                    "partial sums added on the CUDA cores every 48 MMAs",
          "tiled": "FP32 FMA on the CUDA cores, taps added in the reference's (ic, r, s) order",
          "generic": "FP32 FMA on the CUDA cores", "depthwise": "FP32 FMA on the CUDA cores"}
@@ -419,7 +422,8 @@ def main():
         for l in layers:
             L = l["L"]
             rec = {}
-            for name, v in (("tiled_ms", tb.VARIANT_TILED), ("tensor_ms", tb.VARIANT_TENSOR)):
+            for name, v in (("tiled_ms", tb.VARIANT_TILED), ("tensor_ms", tb.VARIANT_TENSOR),
+                            ("tensor16_ms", tb.VARIANT_TENSOR16)):
                 try:
                     rec[name] = tb.timing_sparse_conv2d(l["f"], l["x"], l["y"], batch, L.H, L.W, L.stride, L.pad,
                                                         cuda_stream=stream, variant=v, warm=2, repeat=5) \

@@ -58,9 +58,15 @@ enum {
   TETRIS_VARIANT_TILED = 2,   /* shared-memory tile, per-channel weight lists          */
                               /* 3 is retired (a jump-table interpreter kernel that measured
                                  slower than the list kernel); it is refused as invalid      */
-  TETRIS_VARIANT_TENSOR = 4   /* dense contraction on the tensor cores (tcgen05, split TF32);
+  TETRIS_VARIANT_TENSOR = 4,  /* dense contraction on the tensor cores (tcgen05, split TF32);
                                  strides 1-8; in_channel <= 4, or a multiple of 4 with a
                                  16-byte aligned input                                    */
+  TETRIS_VARIANT_TENSOR16 = 5 /* the same contraction in split FP16 (two 11-bit halves per
+                                 operand, FP32 accumulate: FP32-accurate at twice the tensor
+                                 rate); stride 1, in_channel a multiple of 4 and >= 8, 16-byte
+                                 aligned input.  A launch whose largest |activation| is 2048
+                                 or more (NaN, infinity) or below 2^-8 is recomputed on the
+                                 device by the split-TF32 variant queued behind it         */
 };
 
 typedef struct tetris_filter tetris_filter_t; /* opaque; owns device buffers */

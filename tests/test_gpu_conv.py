@@ -13,7 +13,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
-VARIANTS = {"auto": 0, "generic": 1, "tiled": 2, "tensor": 4}
+VARIANTS = {"auto": 0, "generic": 1, "tiled": 2, "tensor": 4, "tensor16": 5}
 
 
 def device_conv(tb, torch, f, x_nchw, stride, pad, variant=0, poison=True):
@@ -30,7 +30,10 @@ def device_conv(tb, torch, f, x_nchw, stride, pad, variant=0, poison=True):
 
 
 def covers(variant, ks, stride, ic=4):
-    """The tensor-core variant needs in_channel to be a multiple of 4, or at most 4."""
+    """The tensor-core variant needs in_channel to be a multiple of 4, or at most 4; its
+    split-FP16 form stride 1 and in_channel a multiple of 4, at least 8."""
+    if variant == "tensor16":
+        return stride == 1 and ic % 4 == 0 and ic >= 8 and ks <= 7
     if variant == "tensor":
         return ic % 4 == 0 or ic <= 4
     return True
@@ -43,7 +46,7 @@ def check(oracle, got, want):
     return max_rel
 
 
-@pytest.mark.parametrize("variant", ["generic", "tiled", "tensor"])
+@pytest.mark.parametrize("variant", ["generic", "tiled", "tensor", "tensor16"])
 @pytest.mark.parametrize("path", GOLDEN, ids=lambda p: os.path.basename(p)[:-4])
 def test_golden_vectors(tb, torch_cuda, oracle, path, variant):
     z = np.load(path)
@@ -93,7 +96,7 @@ SEEDED = [
 ]
 
 
-@pytest.mark.parametrize("variant", ["generic", "tiled", "tensor"])
+@pytest.mark.parametrize("variant", ["generic", "tiled", "tensor", "tensor16"])
 @pytest.mark.parametrize("case", SEEDED, ids=lambda c: "n%d_ic%d_%dx%d_oc%d_k%d_s%d_p%d" % c[:8])
 def test_seeded_cases_against_oracle(tb, torch_cuda, oracle, case, variant):
     n, ic, h, w, oc, ks, stride, pad, density, K, TIC = case
@@ -121,7 +124,7 @@ def test_skewed_rows_and_empty_channels(tb, torch_cuda, oracle):
     x = rng.standard_normal((2, ic, 20, 20)).astype(np.float32)
     f = tb.SparseFilter(filt, ic, oc, 3)
     want = oracle.host_conv2d(x, filt, 1, 1)
-    for v in (1, 2, 4):
+    for v in (1, 2, 4, 5):
         got = device_conv(tb, torch_cuda, f, x, 1, 1, v)
         check(oracle, got, want)
         assert np.all(got[:, [5, 40, 95]] == 0)
@@ -250,14 +253,14 @@ def test_auto_choice_reports_the_kernel_an_automatic_launch_uses(tb, torch_cuda,
     f = tb.SparseFilter(filt, 128, 128, 3)
     x = rng.random((4, 128, 28, 28), dtype=np.float32)
     choice = tb.auto_choice(f, 4, 28, 28, 1, 1)
-    assert choice == tb.VARIANT_TENSOR
+    assert choice in (tb.VARIANT_TENSOR, tb.VARIANT_TENSOR16)
     got = device_conv(tb, torch_cuda, f, x, 1, 1, 0)
     check(oracle, got, oracle.host_conv2d(x, filt, 1, 1))
     # after tuning the answer is whichever kernel was faster when timed; it must be one of the two
     xin = torch_cuda.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
     out = torch_cuda.empty(4, 28, 28, 128, device="cuda")
     tb.tune_sparse_conv2d(f, xin, out, 4, 28, 28, 1, 1, max_candidates=4)
-    assert tb.auto_choice(f, 4, 28, 28, 1, 1) in (tb.VARIANT_TILED, tb.VARIANT_TENSOR)
+    assert tb.auto_choice(f, 4, 28, 28, 1, 1) in (tb.VARIANT_TILED, tb.VARIANT_TENSOR, tb.VARIANT_TENSOR16)
 
 
 @pytest.mark.parametrize("seed", range(10))
@@ -328,7 +331,7 @@ def test_tensor_variant_against_list_kernel_many_shapes(tb, torch_cuda):
         assert agree(ref, y)
 
 
-@pytest.mark.parametrize("variant", ["generic", "tiled", "tensor", "auto"])
+@pytest.mark.parametrize("variant", ["generic", "tiled", "tensor", "tensor16", "auto"])
 def test_output_offset_by_one_float(tb, torch_cuda, oracle, variant):
     """An output that is only 4-byte aligned (a view one float into a buffer) is legal: the
     kernels must leave their 16-byte stores and adds for such a pointer."""
@@ -364,3 +367,109 @@ def test_auto_falls_back_when_no_list_tile_fits(tb, torch_cuda, oracle):
     assert tb.auto_choice(f, 2, 20, 20, 1, 3) in (tb.VARIANT_TENSOR, tb.VARIANT_GENERIC, tb.VARIANT_TILED)
     got = device_conv(tb, torch_cuda, f, x, 1, 3, VARIANTS["auto"])
     check(oracle, got, oracle.host_conv2d(x, filt, 1, 3))
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_tensor16_random_shapes(tb, torch_cuda, oracle, seed):
+    """Ragged shapes for the split-FP16 tensor-core variant: partial K chunks and channel tiles,
+    1x1 (with and without padding) to 7x7 filters, images smaller and larger than a tile, several
+    images per tile, tall and wide images, outputs that are not a multiple of four channels."""
+    rng = np.random.default_rng(3000 + seed)
+    ks = int(rng.choice([1, 1, 3, 3, 3, 5, 7]))
+    pad = int(rng.integers(0, ks)) if seed % 2 else ks // 2
+    ic = 4 * int(rng.integers(2, 70))
+    oc = int(rng.choice([1, 3, 30, 64, 65, 128, 130, 200, 256]))
+    h = int(rng.integers(ks, 45))
+    w = int(rng.integers(ks, 45))
+    n = int(rng.integers(1, 7))
+    filt = rng.normal(0, 0.05, (oc, ic, ks, ks)).astype(np.float32)
+    filt[rng.random(filt.shape) < rng.choice([0.0, 0.7, 0.95])] = 0
+    x = rng.random((n, ic, h, w), dtype=np.float32) - 0.3
+    f = tb.SparseFilter(filt, ic, oc, ks)
+    got = device_conv(tb, torch_cuda, f, x, 1, pad, VARIANTS["tensor16"])
+    check(oracle, got, oracle.host_conv2d(x, filt, 1, pad))
+
+
+def test_tensor16_value_ranges(tb, torch_cuda, oracle):
+    """Split FP16 keeps FP32 accuracy over the range FP16 can hold -- large activations (up to
+    ~3e4), tiny ones (1e-7: below FP16's normal range, the absolute error stays far under the
+    floor), weights of very different magnitudes (|w| from 1e-6 to 30) -- and a launch whose
+    activations do not fit FP16's window (2048 and more, or all below 2^-8) is recomputed by the
+    split-TF32 variant behind it: every case has to meet the bar of the path, with the absolute
+    floor scaled like the activations."""
+    torch = torch_cuda
+    rng = np.random.default_rng(77)
+    n, ic, h, oc = 2, 96, 20, 72
+    filt = rng.normal(0, 0.05, (oc, ic, 3, 3)).astype(np.float32)
+    filt[rng.random(filt.shape) < 0.8] = 0
+    base = rng.random((n, ic, h, h), dtype=np.float32)
+    f = tb.SparseFilter(filt, ic, oc, 3)
+    for scale in (1.0, 64.0, 2000.0, 3.0e4, 1.0e-2, 1.0e-7, 1.0e5):
+        x = (base * np.float32(scale)).astype(np.float32)
+        got = device_conv(tb, torch_cuda, f, x, 1, 1, VARIANTS["tensor16"])
+        want = oracle.host_conv2d(x, filt, 1, 1)
+        # the bar of the path, with its absolute floor scaled like the data
+        bad, max_rel, _ = oracle.compare(got / np.float32(scale), want / np.float32(scale))
+        assert bad == 0, "activations x %g: %d elements off (max rel %.3g)" % (scale, bad, max_rel)
+    mixed = base.copy()                          # tiny and ordinary activations side by side
+    mixed[:, ::2] *= np.float32(1e-6)
+    got = device_conv(tb, torch_cuda, f, mixed, 1, 1, VARIANTS["tensor16"])
+    bad, max_rel, _ = oracle.compare(got, oracle.host_conv2d(mixed, filt, 1, 1))
+    assert bad == 0, "tiny and ordinary activations mixed: %d elements off (max rel %.3g)" % (bad, max_rel)
+    x = base.copy()                              # after an out-of-range launch the next one is a plain FP16 launch again
+    got = device_conv(tb, torch_cuda, f, x, 1, 1, VARIANTS["tensor16"])
+    bad, max_rel, _ = oracle.compare(got, oracle.host_conv2d(x, filt, 1, 1))
+    assert bad == 0, "plain launch after an out-of-range one: %d elements off (max rel %.3g)" % (bad, max_rel)
+    wide = filt * np.exp(rng.uniform(np.log(2e-5), np.log(600.0), (oc, 1, 1, 1))).astype(np.float32)
+    f2 = tb.SparseFilter(wide, ic, oc, 3)
+    got = device_conv(tb, torch_cuda, f2, base, 1, 1, VARIANTS["tensor16"])
+    want = oracle.host_conv2d(base, wide, 1, 1)
+    bad, max_rel, _ = oracle.compare(got, want)
+    err = np.abs(got - want) - (1e-4 * np.maximum(np.abs(got), np.abs(want)) + 1e-5)
+    worst = np.unravel_index(np.argmax(err), got.shape)
+    assert bad == 0, "weights of very different magnitudes: %d elements off (max rel %.3g), worst at %s: %g vs %g" % (
+        bad, max_rel, worst, got[worst], want[worst])
+
+
+def test_tensor16_against_tensor_many_shapes_and_repeats(tb, torch_cuda):
+    """Forty seeded mid-size shapes, split-FP16 against the list kernel on the device; then a
+    full-size layer launched ten times: a race in the pipeline shows up as a launch that differs."""
+    torch = torch_cuda
+    rng = np.random.default_rng(2025)
+
+    def agree(ya, yb):
+        err = (ya - yb).abs()
+        return not bool((((err > 1e-4 * ya.abs()) & (err > 1e-5)) | torch.isnan(yb)).any())
+
+    for _ in range(40):
+        ks = int(rng.choice([1, 3, 3, 3, 5]))
+        pad = int(rng.integers(0, ks))
+        ic = int(rng.choice([8, 32, 64, 96, 128, 160, 256, 512]))
+        oc = int(rng.choice([16, 64, 100, 128, 192, 256, 384]))
+        h, w = int(rng.integers(max(ks, 7), 70)), int(rng.integers(max(ks, 7), 70))
+        n = int(rng.integers(1, 20))
+        filt = rng.normal(0, 0.05, (oc, ic, ks, ks)).astype(np.float32)
+        filt[rng.random(filt.shape) < rng.choice([0.5, 0.8, 0.95])] = 0
+        f = tb.SparseFilter(filt, ic, oc, ks)
+        oh, ow = tb.out_extent(h, ks, 1, pad), tb.out_extent(w, ks, 1, pad)
+        x = torch.rand(n, h, w, ic, device="cuda") - 0.3
+        ya = torch.full((n, oh, ow, oc), float("nan"), device="cuda")
+        yb = torch.full((n, oh, ow, oc), float("nan"), device="cuda")
+        tb.sparse_conv2d(f, x, ya, n, h, w, 1, pad, variant=tb.VARIANT_TILED)
+        tb.sparse_conv2d(f, x, yb, n, h, w, 1, pad, variant=tb.VARIANT_TENSOR16)
+        torch.cuda.synchronize()
+        f.check()
+        assert agree(ya, yb), dict(ks=ks, pad=pad, ic=ic, oc=oc, h=h, w=w, n=n)
+
+    filt = rng.normal(0, 0.05, (256, 128, 3, 3)).astype(np.float32)
+    filt[rng.random(filt.shape) < 0.85] = 0
+    f = tb.SparseFilter(filt, 128, 256, 3)
+    x = torch.rand(16, 56, 56, 128, device="cuda")
+    ref = torch.empty(16, 56, 56, 256, device="cuda")
+    tb.sparse_conv2d(f, x, ref, 16, 56, 56, 1, 1, variant=tb.VARIANT_TILED)
+    for _ in range(10):
+        y = torch.full((16, 56, 56, 256), float("nan"), device="cuda")
+        tb.sparse_conv2d(f, x, y, 16, 56, 56, 1, 1, variant=tb.VARIANT_TENSOR16)
+        torch.cuda.synchronize()
+        f.check()
+        assert agree(ref, y)

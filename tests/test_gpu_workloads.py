@@ -68,6 +68,8 @@ def _variants(tb, L):
     v = [("auto_tuned", tb.VARIANT_AUTO, True), ("tiled", tb.VARIANT_TILED, False)]
     if L.IC % 4 == 0 or L.IC <= 4:
         v.append(("tensor", tb.VARIANT_TENSOR, False))
+    if L.stride == 1 and L.IC % 4 == 0 and L.IC >= 8:
+        v.append(("tensor16", tb.VARIANT_TENSOR16, False))
     return v
 
 

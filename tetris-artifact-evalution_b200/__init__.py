@@ -31,7 +31,7 @@ LIB_PATH = os.path.join(_HERE, "libtetris_b200.so")
 WARM = 30     # Tetris/tensor_utils.h:11
 REPEAT = 100  # Tetris/tensor_utils.h:10
 
-VARIANT_AUTO, VARIANT_GENERIC, VARIANT_TILED, VARIANT_TENSOR = 0, 1, 2, 4  # 3 was an interpreter kernel, removed
+VARIANT_AUTO, VARIANT_GENERIC, VARIANT_TILED, VARIANT_TENSOR, VARIANT_TENSOR16 = 0, 1, 2, 4, 5  # 3 is retired
 
 _c_float_p = ctypes.POINTER(ctypes.c_float)
 _c_int_p = ctypes.POINTER(ctypes.c_int)

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtetris_b200.so")
-SOURCES = ["api.cu", "compress.cu", "conv_generic.cu", "conv_tiled.cu", "conv_tc.cu", "depthwise.cu", "layout.cu",
+SOURCES = ["api.cu", "compress.cu", "conv_generic.cu", "conv_tiled.cu", "conv_tc.cu", "conv_tc16.cu", "depthwise.cu", "layout.cu",
            "noalloc.cu", "serialize.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

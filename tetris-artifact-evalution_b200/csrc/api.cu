@@ -79,6 +79,7 @@ int dispatch(const tetris_filter *f, const float *in, float *out, const ConvShap
     case TETRIS_VARIANT_GENERIC: return launch_conv_generic(f, in, out, s, st);
     case TETRIS_VARIANT_TILED: return launch_conv_tiled(f, in, out, s, st, false);
     case TETRIS_VARIANT_TENSOR: return launch_conv_tc(f, in, out, s, st);
+    case TETRIS_VARIANT_TENSOR16: return launch_conv_tc16(f, in, out, s, st);
     case TETRIS_VARIANT_AUTO: {
       // the list kernel (which may hand over to the tensor-core variant); when no tile geometry of
       // it fits shared memory (long list pieces of a dense, large filter with a caller-chosen
@@ -263,7 +264,7 @@ int tetris_filter_create_ex(const float *filter_oihw, int in_channel, int out_ch
   if ((rc = compress_fill(d_dense, in_channel, out_channel, kernel_size, K, TIC, B, T,
                           f->d_prog_offsets, f->d_ops, f->n_ops, 0)))
     return fail(rc);
-  if ((rc = conv_tc_prepare(f, d_dense))) return fail(rc);
+  if ((rc = conv_tc_prepare(f, d_dense)) || (rc = conv_tc16_prepare(f, d_dense))) return fail(rc);
   if (cudaDeviceSynchronize() != cudaSuccess) {
     set_error("compressor fill failed: %s", cudaGetErrorString(cudaGetLastError()));
     return fail(TETRIS_ERR_CUDA);
@@ -283,6 +284,7 @@ void tetris_filter_destroy(tetris_filter_t *f) {
   cudaFree(f->d_list_offsets);
   tiled_plan_cache_delete(f->plan_cache);
   conv_tc_state_delete(f->tc_state);
+  conv_tc16_state_delete(f->tc16_state);
   cudaFree(f->d_dense);
   delete f;
 }
@@ -345,7 +347,7 @@ int tetris_filter_check(const tetris_filter_t *f) {
     set_error("device error: %s", cudaGetErrorString(cudaGetLastError()));
     return TETRIS_ERR_CUDA;
   }
-  if (conv_tc_check_error(f)) {
+  if (conv_tc_check_error(f) | conv_tc16_check_error(f)) {
     set_error("a tensor-core launch of this filter gave up on a bounded barrier wait; its output is invalid");
     return TETRIS_ERR_CUDA;
   }

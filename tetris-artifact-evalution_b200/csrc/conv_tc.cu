@@ -115,6 +115,7 @@ struct TcParams {
   int ksplit;                  // work items per tile: each takes n_chunks / ksplit chunks and adds its result in
   int *error_flag;
   const float *w_tiles;        // weight tile images, see tc_weight_tiles_kernel
+  unsigned *gate;              // when set: the launch runs only if the magnitude in gate[0] asks for it (see launch_conv_tc_gated)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -205,6 +206,25 @@ template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
   extern __shared__ unsigned char smem_raw[];
+  // A gated launch stands behind the split-FP16 variant, which left the largest |activation| it
+  // saw (FP32 bits) in gate[0].  Recompute the layer when that does not fit FP16's window
+  // (2048 or more after the variant's scaling, NaN, infinity) or when all activations are so
+  // small (below 2^-8, not all zero) that FP16's absolute error would show; return otherwise.
+  // Every CTA reads the word before it counts itself in gate[1]; the last one to do so clears
+  // both for the next launch.
+  if (p.gate) {
+    unsigned *verdict = reinterpret_cast<unsigned *>(smem_raw);
+    if (threadIdx.x == 0) {
+      const unsigned m = *reinterpret_cast<volatile unsigned *>(p.gate);
+      *verdict = (m >= 0x45000000u || (m != 0u && m < 0x3B800000u)) ? 1u : 0u;
+      __threadfence();
+      if (atomicAdd(p.gate + 1, 1u) == gridDim.x - 1) { p.gate[0] = 0u; p.gate[1] = 0u; }
+    }
+    __syncthreads();
+    const unsigned run = *verdict;
+    __syncthreads();
+    if (!run) return;
+  }
   unsigned char *xbase = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
   unsigned char *wbase = xbase + kXBytes;
   unsigned char *store_base = wbase + 4 * 2 * kTileBytes;  // = weight stage 4, unused when w_stages == 4
@@ -734,6 +754,7 @@ struct TcState {
   // four -- finds its map again instead of encoding one per launch.  Round-robin replacement.
   struct Setup {
     bool valid = false;
+    bool gated = false;          // set-ups of gated launches never split the K range
     const float *in = nullptr;
     ConvShape shape{};
     CUtensorMap map_x;
@@ -791,7 +812,27 @@ bool conv_tc_supported(const tetris_filter *f, const ConvShape &s) {
   return static_cast<TcState *>(f->tc_state)->folded || (s.IC & 3) == 0;
 }
 
+namespace {
+int launch_conv_tc_impl(const tetris_filter *f, const float *in, float *out, const ConvShape &s, cudaStream_t st,
+                        unsigned *gate);
+}
+
 int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const ConvShape &s, cudaStream_t st) {
+  return launch_conv_tc_impl(f, in, out, s, st, nullptr);
+}
+
+// The same launch, conditional on the device: the kernel decides from gate[0] whether to run (see
+// the kernel's first lines).  Such a launch never splits a tile's K range (the zeroing of the
+// output that the split needs cannot be made conditional), so it overwrites the whole output
+// when it runs.
+int launch_conv_tc_gated(const tetris_filter *f, const float *in, float *out, const ConvShape &s, cudaStream_t st,
+                         unsigned *gate) {
+  return launch_conv_tc_impl(f, in, out, s, st, gate);
+}
+
+namespace {
+int launch_conv_tc_impl(const tetris_filter *f, const float *in, float *out, const ConvShape &s, cudaStream_t st,
+                        unsigned *gate) {
   TcState *t = static_cast<TcState *>(f->tc_state);
   if (!conv_tc_supported(f, s) || (!t->folded && (reinterpret_cast<uintptr_t>(in) & 15) != 0)) {
     set_error("tensor-core variant covers strides up to 8, in_channel <= 4 or a multiple of 4, 16-byte aligned inputs");
@@ -806,7 +847,7 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
     TcState::Setup *su = nullptr;
     for (TcState::Setup &c : t->setups) {
       const ConvShape &l = c.shape;
-      if (c.valid && c.in == in && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S) { su = &c; break; }
+      if (c.valid && c.in == in && c.gated == (gate != nullptr) && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S) { su = &c; break; }
     }
     if (!su) {
       su = &t->setups[t->next_setup];
@@ -868,7 +909,7 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
       const double zeroing = ((double)s.N * s.OH * s.OW * s.OC * 4 / 6.0e12 + 3e-6) * 1.9e9 / 1450.0;
       int best_d = 1;
       double best_cost = std::ceil((double)tiles / sms) * (iters + 10.0);
-      for (int d = 2; d <= 8 && d <= q.n_chunks && !f->deterministic; ++d) {
+      for (int d = 2; d <= 8 && d <= q.n_chunks && !f->deterministic && !gate; ++d) {
         if (q.n_chunks % d) continue;
         const double cost = std::ceil((double)tiles * d / sms) * (iters / d + 10.0) + zeroing;
         if (cost < 0.96 * best_cost) { best_cost = cost; best_d = d; }
@@ -880,6 +921,7 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
       const long long total = tiles * best_d;
       su->grid = dim3((unsigned)std::min<long long>(total, sms));  // persistent: one CTA per SM
       su->in = in;
+      su->gated = gate != nullptr;
       su->shape = s;
       su->valid = true;
     }
@@ -890,6 +932,7 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
   }
   p.out = out;
   p.in = in;
+  p.gate = gate;
   const size_t smem = (size_t)kSmemTiles + 1024 + kNumBars * 8 + 16;
   static thread_local bool configured[16] = {false};
   int dev = 0;
@@ -906,9 +949,10 @@ int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const Co
   else
     conv_tc_kernel<128><<<grid, kThreads, smem, st>>>(map_x, p);
   TETRIS_CUDA_TRY(cudaGetLastError());
-  count_launch();
+  if (!gate) count_launch();
   return TETRIS_OK;
 }
+}  // namespace
 
 // 0 = no timeout seen so far, 1 = a bounded wait gave up in some launch (the flag is cleared).
 int conv_tc_check_error(const tetris_filter *f) {

@@ -1,0 +1,864 @@
+// Dense contraction on the 5th-generation tensor cores in SPLIT FP16: the stride-1 layers' fast
+// variant (tcgen05.mma kind::f16 + tcgen05.cp + TMEM + TMA).
+//
+// Arithmetic.  x = x_hi + x_lo and w' = w * 2^sh = w_hi + w_lo with *_hi the value rounded to
+// FP16 (11 significant bits) and *_lo the FP16-rounded remainder; D += x_hi*w_hi + x_lo*w_hi +
+// x_hi*w_lo in FP32 accumulators, scaled back by 2^-sh (exact) at the store.  The products are
+// exact in FP32; what is dropped is x_lo*w_lo and the rounding of the remainders, about 2^-22 of
+// a product each -- the same as the split-TF32 variant (conv_tc.cu), at twice the tensor-core
+// rate and half the operand bytes.  sh is chosen per filter so that the largest |w'| is about
+// 2^13: weights down to 2^-17 of the largest keep a normal FP16 remainder.  Activations are
+// scaled by a fixed 16 (their range is not known before the launch), which puts FP16's window at
+// |x| < 2048 with remainders exact down to |x| = 2^-7 and an absolute error of at most 2e-9 per
+// activation below that.  The conversion warps record the largest magnitude of the launch in
+// global memory; the launcher has queued the split-TF32 variant behind this kernel, which
+// starts, reads that maximum and recomputes the whole layer when it is 2048 or more (or NaN or
+// infinity) -- FP16 would overflow -- or below 2^-8 -- all activations so small that the
+// absolute error above would show in the relative accuracy -- and returns at once otherwise.
+// Results are therefore FP32-accurate for any input.
+//
+// As in the split-TF32 variant the tensor core accumulates 48 MMAs (8 K steps) from zero into a
+// partial accumulator and CUDA-core warps add the partials to a running sum in registers (the
+// tensor core truncates when it adds into its accumulator; see conv_tc.cu).
+//
+// Structure.  GEMM view: M = 128 pixels = 16 groups of 8 consecutive output columns, N = 128
+// (64) output channels, K = (32-channel chunk, filter tap).  What differs from conv_tc.cu is how
+// the M-side operand reaches tensor memory.  There, converter warps rebuild the operand of every
+// tap from the activation patch (nine times per patch for a 3x3 filter) and that conversion, not
+// the tensor pipe, set the pace.  Here the patch is converted ONCE, in place, in shared memory
+// (each 128-byte row of 32 FP32 channels becomes 32 x_hi and 32 x_lo FP16 values), and the
+// operand of a tap is a WINDOW of the converted patch: tcgen05.cp copies 128 rows x 32 bytes from
+// shared to tensor memory through a matrix descriptor whose start address is shifted by the
+// tap's (row, column) offset and whose 8-row groups are PW rows apart (PW = patch width).  The
+// 128-byte swizzle is a function of the shared-memory address, so a window that starts at any
+// 128-byte row reads back exactly what the TMA load and the in-place conversion wrote.
+//   * warp 0 (one thread): one TMA load per 32-channel chunk of the tile's pixels with their
+//     halo (4-D box, out-of-range coordinates zero-filled = the padding) into a ring of stages;
+//   * warps 4-7: convert a landed patch in place, one 128-byte row per thread, conflict-free;
+//   * warp 3 (one elected lane): per K step four tcgen05.cp (x_hi and x_lo, two K slices each)
+//     into one of four operand blocks; per PAIR of K steps one wait (the MMAs that read the block
+//     four pairs ago are done) and one commit;
+//   * warp 2 (one thread): one bulk copy per pair of K steps of prepared {w_hi, w_lo} tile images;
+//   * warp 1 (one elected lane): 6 tcgen05.mma per K step; per pair two waits (operands copied,
+//     weights landed) and one commit.  The pipeline's unit is a pair of K steps because a wait
+//     costs a warp ~200 clocks and a commit ~250, against ~450 for the pair's twelve MMAs;
+//   * warps 8-15: partial accumulators -> running sum in registers -> staged, coalesced stores.
+// Every barrier wait is bounded; on a timeout an error flag is raised, all roles drain, TMEM is
+// freed and the kernel returns; the host reports TETRIS_ERR_CUDA.
+//
+// 1x1 filters take the same pipeline with M = 128 consecutive pixels of the flattened image
+// (no halo, 100 % full tiles).  Covers stride 1, IC % 4 == 0 (TMA strides), KS <= 7.
+// No cluster launch: every load is issued by one CTA for itself.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <cstdlib>
+#include <mutex>
+
+#include "internal.h"
+
+namespace tetris {
+namespace {
+
+constexpr int BM = 128, KC = 32;         // tile rows (pixels); K chunk (32 channels)
+constexpr int kTW = 8, kTH = 16;         // a tile is 16 groups of 8 output columns
+constexpr int kAStages = 4;              // operand blocks in tensor memory: one per pair of K steps, 64 columns each
+constexpr int kACols = 64;               // per K step {x_hi k0, x_hi k1, x_lo k0, x_lo k1} x 8 columns
+constexpr int kTmemCols = 512;           // 2 partial accumulators (<= 128 columns each) + 8 x 32 operand columns
+constexpr int kTmemA = 256;
+constexpr int kWStagesMax = 4, kXStagesMax = 6;   // weight stages hold a pair of K steps
+constexpr int kGroups = 16;              // "pair done" barriers in rotation (a power of two, 2^4: see wait_pair)
+constexpr int kSuper = 4;                // pairs (8 K steps, 48 MMAs) accumulated on the tensor core before the FP32 add outside
+constexpr int kThreads = 512;            // warp 0 x loads, 1 MMA, 2 w loads, 3 cp, 4-7 convert, 8-15 sum + store
+constexpr int kStoreBytes = 8 * 4096;    // store staging: per summing warp 32 rows x 32 channels
+constexpr int kNumBars = 3 * kXStagesMax + kWStagesMax + 2 * kAStages + kGroups + 2;
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr float kXScale = 16.f;          // activations are multiplied by this before the split (undone in out_scale)
+
+struct Tc16Params {
+  float *out;
+  int N, OH, OW, OC, P, KS;
+  int linear;                  // 1x1 filters: a tile is 128 consecutive pixels of the flattened N*OH*OW image
+  int PW;                      // patch width in pixels (kTW + KS - 1); 8 in linear mode
+  int PHI;                     // patch rows one image occupies in a stage
+  int TH, NB;                  // output rows and images of a tile
+  int box_rows;                // 128-byte rows a patch load delivers
+  int x_stage_bytes, n_x;      // activation stage size and ring depth
+  int n_w;                     // weight ring depth
+  int tiles_w, tiles_h, tiles_n;
+  int n_chunks, ksplit;
+  long long total_pixels;      // N * OH * OW (linear mode)
+  float out_scale;             // 2^-sh
+  int *error_flag;
+  unsigned *gate;              // gate[0]: largest |activation| of the launch, as FP32 bits (see launch_conv_tc_gated)
+  const __half *w_tiles;
+  long long *prof;             // debugging: per-role clock totals of CTA 0 (nullptr = off)
+  int dbg;                     // debugging: parts of the pipeline switched off (results are wrong then)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Gives up when the limit is hit or when another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63) == 63) {
+      if (*abort_flag) return false;
+      __nanosleep(32);
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// K-major operand, 128-byte rows, 128B swizzle; 8-row groups `sbo_bytes` apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t sbo_bytes) {
+  return (uint64_t)((saddr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+  return pred != 0;
+}
+// shared -> tensor memory: 128 rows x 32 bytes into 8 columns
+__device__ __forceinline__ void tmem_cp(uint32_t taddr, uint32_t d_lo, uint32_t d_hi) {
+  asm volatile("{\n.reg .b64 d;\nmov.b64 d, {%1, %2};\ntcgen05.cp.cta_group::1.128x256b [%0], d;\n}" ::"r"(taddr), "r"(d_lo), "r"(d_hi) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem descriptor], FP16 operands, FP32 accumulate
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t db_lo, uint32_t db_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\n.reg .b64 d;\nmov.b64 d, {%2, %3};\nsetp.ne.b32 p, %5, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], d, %4, p;\n}"
+               ::"r"(tmem_d), "r"(tmem_a), "r"(db_lo), "r"(db_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *xbase = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+  unsigned char *wbase = xbase + (size_t)p.n_x * p.x_stage_bytes;
+  constexpr int kWBytes = BN * 128;      // weights of one K step: BN rows of {w_hi (64 B), w_lo (64 B)}; a stage holds two
+  unsigned char *store_base = wbase + (size_t)p.n_w * 2 * kWBytes;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(store_base + kStoreBytes);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  auto bar_xfull = [&](int s) { return smem_u32(&bars[s]); };
+  auto bar_xconv = [&](int s) { return smem_u32(&bars[kXStagesMax + s]); };
+  auto bar_xempty = [&](int s) { return smem_u32(&bars[2 * kXStagesMax + s]); };
+  auto bar_wfull = [&](int s) { return smem_u32(&bars[3 * kXStagesMax + s]); };
+  auto bar_afull = [&](int s) { return smem_u32(&bars[3 * kXStagesMax + kWStagesMax + s]); };
+  auto bar_ready = [&](int s) { return smem_u32(&bars[3 * kXStagesMax + kWStagesMax + kAStages + s]); };
+  auto bar_gdone = [&](int c) { return smem_u32(&bars[3 * kXStagesMax + kWStagesMax + 2 * kAStages + c]); };
+  auto bar_pempty = [&](int b) { return smem_u32(&bars[kNumBars - 2 + b]); };
+
+  if (tid == 0) {
+    for (int s = 0; s < kXStagesMax; ++s) { mbar_init(bar_xfull(s), 1); mbar_init(bar_xconv(s), 4); mbar_init(bar_xempty(s), 1); }
+    for (int s = 0; s < kWStagesMax; ++s) mbar_init(bar_wfull(s), 1);
+    for (int s = 0; s < kAStages; ++s) { mbar_init(bar_afull(s), 1); mbar_init(bar_ready(s), 1); }
+    for (int c = 0; c < kGroups; ++c) mbar_init(bar_gdone(c), 1);
+    for (int b = 0; b < 2; ++b) mbar_init(bar_pempty(b), 8);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // the whole tensor memory of the SM: this kernel runs one CTA per SM
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  // debugging aid: clocks spent per role in total ([role * 8]) and inside each kind of wait
+  const bool prof_on = p.prof != nullptr && blockIdx.x == 0;
+  long long pw[7] = {0, 0, 0, 0, 0, 0, 0};
+  const long long prof_t0 = prof_on ? clock64() : 0;
+#define TIMED(slot, expr) ([&]() { const long long t0_ = prof_on ? clock64() : 0; const bool r_ = (expr); if (prof_on) pw[slot] += clock64() - t0_; return r_; }())
+#define PROF_OUT(role) do { if (prof_on && lane == 0) { p.prof[(role) * 8] = clock64() - prof_t0; for (int i_ = 0; i_ < 7; ++i_) p.prof[(role) * 8 + 1 + i_] = pw[i_]; } } while (0)
+
+  // Persistent CTA: work items blockIdx.x, blockIdx.x + gridDim.x, ...; the channel tile is the
+  // fastest index, so CTAs that run side by side read the same activation patch.
+  const int taps = p.KS * p.KS;
+  const int item_chunks = p.n_chunks / p.ksplit;          // chunks of a work item (ksplit divides n_chunks)
+  const int iters = taps * item_chunks;                   // K steps of a work item
+  const int npairs = (iters + 1) / 2;                     // the pipeline's unit is a PAIR of K steps (the last may be single)
+  const int tile_supers = (npairs + kSuper - 1) / kSuper; // partial accumulators of a work item
+  const int oc_tiles = (p.OC + BN - 1) / BN;
+  const int total_items = p.tiles_w * p.tiles_h * p.tiles_n * oc_tiles * p.ksplit;
+  auto decode = [&](int t, int &w0, int &h0, int &n0, int &oc0, int &chunk0) {
+    chunk0 = (t % p.ksplit) * item_chunks; t /= p.ksplit;
+    oc0 = (t % oc_tiles) * BN; t /= oc_tiles;
+    w0 = (t % p.tiles_w) * kTW; t /= p.tiles_w;       // (linear mode: tiles_w = number of 128-pixel tiles)
+    h0 = (t % p.tiles_h) * p.TH;
+    n0 = (t / p.tiles_h) * p.NB;
+  };
+  // Pair G of this CTA (counted across work items) signals bar_gdone(G % kGroups) when its MMAs
+  // have completed.  Nobody looks at a pair's barrier later than 16 pairs after it: the rings are
+  // 4 pairs deep and the MMAs run at most two partial sums (8 pairs) ahead of the summing warps.
+  auto wait_pair = [&](int G) { return mbar_wait(bar_gdone(G & (kGroups - 1)), (G >> 4) & 1, abort_flag); };
+  auto wait_pair_warp = [&](int G) { return mbar_wait_warp(bar_gdone(G & (kGroups - 1)), (G >> 4) & 1, abort_flag); };
+
+  if (warp == 0) {
+    // ---- activation loads: one patch (tile + halo) per 32-channel chunk ----
+    if (lane == 0) {
+      const uint32_t box_bytes = (uint32_t)p.box_rows * 128u;
+      int s = 0;
+      uint32_t phase = 1;  // (a fresh barrier lets the first lap through)
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
+        int w0, h0, n0, oc0, chunk0;
+        decode(t, w0, h0, n0, oc0, chunk0);
+        for (int chunk = chunk0; chunk < chunk0 + item_chunks; ++chunk) {
+          if (!(ok = TIMED(0, mbar_wait(bar_xempty(s), phase, abort_flag)))) break;
+          mbar_expect_tx(bar_xfull(s), box_bytes);
+          if (p.linear)
+            tma_load_4d(smem_u32(xbase + (size_t)s * p.x_stage_bytes), &map_x, bar_xfull(s), chunk * KC, (w0 / kTW) * BM, 0, 0);
+          else
+            tma_load_4d(smem_u32(xbase + (size_t)s * p.x_stage_bytes), &map_x, bar_xfull(s), chunk * KC, w0 - p.P, h0 - p.P, n0);
+          if (++s == p.n_x) { s = 0; phase ^= 1u; }
+        }
+      }
+      PROF_OUT(0);
+    }
+  } else if (warp == 2) {
+    // ---- weight loads: one bulk copy per pair (the {w_hi, w_lo} images of its K steps lie
+    //      back to back in global memory) ----
+    if (lane == 0) {
+      int G = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
+        int w0, h0, n0, oc0, chunk0;
+        decode(t, w0, h0, n0, oc0, chunk0);
+        const __half *item = p.w_tiles + ((size_t)(oc0 / BN) * p.n_chunks + chunk0) * taps * (size_t)(BN * 64);
+        for (int j = 0; j < npairs; ++j, ++G) {
+          const int s = G % p.n_w;
+          if (G >= p.n_w && !(ok = TIMED(0, wait_pair(G - p.n_w)))) break;
+          const uint32_t bytes = (uint32_t)(min(2, iters - 2 * j) * kWBytes);
+          if ((p.dbg & 2) && G >= p.n_w) { mbar_arrive(bar_wfull(s)); continue; }
+          mbar_expect_tx(bar_wfull(s), bytes);
+          bulk_load(smem_u32(wbase + (size_t)s * 2 * kWBytes), item + (size_t)(2 * j) * (BN * 64), bytes, bar_wfull(s));
+        }
+      }
+      PROF_OUT(1);
+    }
+  } else if (warp == 3) {
+    // ---- operand copies (converged warp, one elected lane issues, so that descriptors and
+    //      addresses stay in uniform registers): per K step four tcgen05.cp -- the tap's window of
+    //      the converted patch -> the step's operand block in tensor memory; one wait and one
+    //      commit per pair.  Everything that depends on the K step is counted along: the issuing
+    //      thread's own instructions, not the tensor unit, set the pace otherwise. ----
+    const uint32_t sbo = (uint32_t)(p.linear ? 1024 : p.PW * 128);
+    const uint32_t da_hi = (uint32_t)(smem_desc(0, sbo) >> 32);
+    const uint32_t x0 = (uint32_t)smem_desc(smem_u32(xbase), sbo);       // descriptor (low word) of stage 0, tap (0, 0)
+    const uint32_t stage_step = (uint32_t)(p.x_stage_bytes >> 4);        // ... one stage further
+    const uint32_t row_step = (uint32_t)((p.PW - p.KS + 1) * 128 >> 4);  // ... from the end of a filter row to the next row
+    int G = 0, sx = 0;
+    uint32_t xd = x0, td = 0;  // descriptor of the current stage; offset of the current tap
+    uint32_t xphase = 0;       // phase of the "converted" barrier of stage sx
+    bool fresh_patch = true;   // the patch in stage sx has not been waited for yet
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
+      int r = 0, q = 0;  // tap of the next K step
+      for (int j = 0; j < npairs; ++j, ++G) {
+        const int sa = G & (kAStages - 1);
+        const bool two = iters - 2 * j >= 2;
+        // the MMAs that read this operand block (four pairs ago) are done
+        if (G >= kAStages && !(ok = TIMED(0, wait_pair_warp(G - kAStages)))) break;
+        // the patch of the pair's first K step is converted (waited for once per patch); that of
+        // the second step, when it is the next patch, below
+        if (fresh_patch) {
+          if (!(ok = TIMED(1, mbar_wait_warp(bar_xconv(sx), xphase, abort_flag)))) break;
+          fresh_patch = false;
+        }
+        if (two && r == p.KS - 1 && q == p.KS - 1) {  // the second step opens the next patch
+          const int nsx = sx + 1 == p.n_x ? 0 : sx + 1;
+          if (!(ok = TIMED(1, mbar_wait_warp(bar_xconv(nsx), nsx == 0 ? xphase ^ 1u : xphase, abort_flag)))) break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t ta = tmem_base + (uint32_t)(kTmemA + sa * kACols), t1 = ta + 32u;
+        const uint32_t a0 = xd + td;
+        const int sx0 = sx;
+        const bool last0 = r == p.KS - 1 && q == p.KS - 1;
+        if (last0) { r = 0; q = 0; td = 0; if (++sx == p.n_x) { sx = 0; xd = x0; xphase ^= 1u; } else xd += stage_step; }
+        else if (++q == p.KS) { q = 0; ++r; td += row_step; }
+        else td += 8;
+        const uint32_t a1 = xd + td;
+        const int sx1 = sx;
+        const bool last1 = two && r == p.KS - 1 && q == p.KS - 1;
+        if (two) {
+          if (last1) { r = 0; q = 0; td = 0; if (++sx == p.n_x) { sx = 0; xd = x0; xphase ^= 1u; } else xd += stage_step; }
+          else if (++q == p.KS) { q = 0; ++r; td += row_step; }
+          else td += 8;
+        }
+        // a step that was the last of its patch leaves the next patch unwaited-for -- unless the
+        // pair's second step already opened (and waited for) it
+        if (last1) fresh_patch = true;
+        else if (last0) fresh_patch = !two;
+        if (elect_one()) {
+          // operand block of a K step: columns 0-7 / 8-15 x_hi of channels 0-15 / 16-31, 16-23 / 24-31 x_lo
+          // (32 bytes along K = 2 in a descriptor's address field)
+          tmem_cp(ta, a0, da_hi); tmem_cp(ta + 8, a0 + 2, da_hi); tmem_cp(ta + 16, a0 + 4, da_hi); tmem_cp(ta + 24, a0 + 6, da_hi);
+          if (last0) umma_commit(bar_xempty(sx0));  // the patch has been read for the last time
+          if (two) {
+            tmem_cp(t1, a1, da_hi); tmem_cp(t1 + 8, a1 + 2, da_hi); tmem_cp(t1 + 16, a1 + 4, da_hi); tmem_cp(t1 + 24, a1 + 6, da_hi);
+            if (last1) umma_commit(bar_xempty(sx1));
+          }
+          umma_commit(bar_afull(sa));
+        }
+        __syncwarp();
+      }
+    }
+    PROF_OUT(2);
+  } else if (warp == 1) {
+    // ---- MMA issue (converged warp, one elected lane): six tcgen05.mma per K step, one wait and
+    //      one commit per pair ----
+    const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    const uint32_t dw_hi = (uint32_t)(smem_desc(0, 1024) >> 32);
+    const uint32_t w0 = (uint32_t)smem_desc(smem_u32(wbase), 1024);
+    int G = 0, sw = 0, sbase = 0, sp = 0;
+    uint32_t wd = w0, wphase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x, sbase += tile_supers) {
+      for (int j = 0, jj = 0, si = 0; j < npairs; ++j, ++G) {
+        const int sa = G & (kAStages - 1);
+        const uint32_t acc0 = jj == 0 ? 0u : 1u;  // the first MMA of a partial overwrites it
+        const uint32_t tmem_d = tmem_base + (uint32_t)(((sbase + si) & 1) * BN);
+        if (jj == 0) {  // first pair of a partial sum: its accumulator has been drained (two partials ago)
+          if (!(ok = TIMED(1, mbar_wait_warp(bar_pempty(sp & 1), ((sp >> 1) & 1) ^ 1, abort_flag)))) break;
+          ++sp;
+        }
+        if (++jj == kSuper) { jj = 0; ++si; }
+        if (!(ok = TIMED(2, mbar_wait_warp(bar_wfull(sw), wphase, abort_flag)))) break;  // the pair's weights have landed
+        if (!(ok = TIMED(0, mbar_wait_warp(bar_afull(sa), (G >> 2) & 1, abort_flag)))) break;  // ... and its operand blocks
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        long long ts0 = prof_on ? clock64() : 0;
+        const bool two = iters - 2 * j >= 2;
+        const uint32_t ta = tmem_base + (uint32_t)(kTmemA + sa * kACols), t1 = ta + 32u;
+        const uint32_t dlo = wd, d1 = wd + (uint32_t)(kWBytes >> 4);
+        if (++sw == p.n_w) { sw = 0; wd = w0; wphase ^= 1u; } else wd += (uint32_t)(2 * kWBytes >> 4);
+        if (elect_one()) {
+          // K slices of 16 channels: 32 bytes = 2 in the address field; w_lo sits 64 bytes after w_hi
+          umma_f16_ts(tmem_d, ta, dlo, dw_hi, idesc, acc0);
+          umma_f16_ts(tmem_d, ta + 16, dlo, dw_hi, idesc, 1u);
+          umma_f16_ts(tmem_d, ta, dlo + 4, dw_hi, idesc, 1u);
+          umma_f16_ts(tmem_d, ta + 8, dlo + 2, dw_hi, idesc, 1u);
+          umma_f16_ts(tmem_d, ta + 24, dlo + 2, dw_hi, idesc, 1u);
+          umma_f16_ts(tmem_d, ta + 8, dlo + 6, dw_hi, idesc, 1u);
+          if (two) {
+            umma_f16_ts(tmem_d, t1, d1, dw_hi, idesc, 1u);
+            umma_f16_ts(tmem_d, t1 + 16, d1, dw_hi, idesc, 1u);
+            umma_f16_ts(tmem_d, t1, d1 + 4, dw_hi, idesc, 1u);
+            umma_f16_ts(tmem_d, t1 + 8, d1 + 2, dw_hi, idesc, 1u);
+            umma_f16_ts(tmem_d, t1 + 24, d1 + 2, dw_hi, idesc, 1u);
+            umma_f16_ts(tmem_d, t1 + 8, d1 + 6, dw_hi, idesc, 1u);
+          }
+          if (prof_on) { const long long n_ = clock64(); pw[3] += n_ - ts0; ts0 = n_; }
+          umma_commit(bar_gdone(G & (kGroups - 1)));
+          if (prof_on) { const long long n_ = clock64(); pw[4] += n_ - ts0; ts0 = n_; }
+        }
+        __syncwarp();
+      }
+    }
+    PROF_OUT(3);
+  } else if (warp >= 4 && warp < 8) {
+    // ---- warps 4..7: a landed patch, in place: each 128-byte row of 32 FP32 channels becomes
+    //      {x_hi[32], x_lo[32]} FP16.  One row per thread: the 16-byte chunks of row r sit at
+    //      chunk ^ (r & 7) before and after, so the eight lanes of a quarter-warp touch eight
+    //      different bank groups. ----
+    const int ct = (warp - 4) * 32 + lane;
+    int u = 0;
+    bool ok = true;
+    uint32_t seen_max = 0;
+    for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
+      for (int chunk = 0; chunk < item_chunks; ++chunk, ++u) {
+        const int sx = u % p.n_x;
+        if (!(ok = TIMED(0, mbar_wait_warp(bar_xfull(sx), (u / p.n_x) & 1, abort_flag)))) break;
+        unsigned char *stage = xbase + (size_t)sx * p.x_stage_bytes;
+        for (int row = ct; row < ((p.dbg & 1) ? 0 : p.box_rows); row += 128) {
+          uint4 *rp = reinterpret_cast<uint4 *>(stage + (size_t)row * 128);
+          const int sw = row & 7;
+          uint4 v[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) v[c] = rp[c ^ sw];
+          uint32_t hi[16], lo[16];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float x0 = kXScale * __uint_as_float(v[c].x), x1 = kXScale * __uint_as_float(v[c].y),
+                        x2 = kXScale * __uint_as_float(v[c].z), x3 = kXScale * __uint_as_float(v[c].w);
+            seen_max = max(seen_max, max(max(v[c].x & 0x7FFFFFFFu, v[c].y & 0x7FFFFFFFu), max(v[c].z & 0x7FFFFFFFu, v[c].w & 0x7FFFFFFFu)));
+            const __half2 h01 = __floats2half2_rn(x0, x1), h23 = __floats2half2_rn(x2, x3);
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            hi[2 * c] = *reinterpret_cast<const uint32_t *>(&h01);
+            hi[2 * c + 1] = *reinterpret_cast<const uint32_t *>(&h23);
+            lo[2 * c] = pack_half2(x0 - f01.x, x1 - f01.y);
+            lo[2 * c + 1] = pack_half2(x2 - f23.x, x3 - f23.y);
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            rp[c ^ sw] = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+            rp[(c + 4) ^ sw] = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+          }
+        }
+        // the writes above go through the generic proxy, tcgen05.cp reads through the async proxy
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_xconv(sx));
+      }
+    }
+    // the launch's largest magnitude: the guard kernel behind this one decides on it
+    for (int d = 16; d; d >>= 1) seen_max = max(seen_max, __shfl_xor_sync(0xffffffffu, seen_max, d));
+    if (lane == 0 && seen_max) atomicMax(p.gate, seen_max);
+    if (warp == 4) PROF_OUT(4);
+  } else if (warp >= 8) {
+    // ---- warps 8..15: running sum in registers, store at the end of the work item ----
+    constexpr int NC = BN / 2;             // channels per thread
+    const int quarter = warp & 3, half = (warp - 8) >> 2;
+    const int row = quarter * 32 + lane;   // tile row = pixel = TMEM lane
+    const int gx = row & 7, grp = row >> 3;
+    const int pn = p.linear ? 0 : grp / p.PHI, ph = p.linear ? 0 : grp - pn * p.PHI;
+    const bool vec = (p.OC & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+    const bool small_out = (unsigned long long)p.N * p.OH * p.OW * p.OC < (1ull << 34);  // 32-bit offsets in 16-byte units
+    int gbase = 0, sp = 0;  // first pair of the item; partial sum, counted across items
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x, gbase += npairs) {
+      float acc[NC];
+#pragma unroll
+      for (int j = 0; j < NC; ++j) acc[j] = 0.f;
+      for (int si = 0; si < tile_supers; ++si, ++sp) {
+        const int b = sp & 1;
+        if (!(ok = TIMED(0, wait_pair_warp(gbase + min((si + 1) * kSuper, npairs) - 1)))) break;  // the partial's last pair
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + half * NC);
+#pragma unroll
+        for (int c0 = 0; c0 < NC; c0 += 16) {
+          uint32_t v[16];
+          if (p.dbg & 4) { for (int j = 0; j < 16; ++j) v[j] = 0; } else tmem_ld16(taddr + c0, v);
+          if (c0 + 16 == NC) {  // everything is in registers: the tensor core may overwrite the partial
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_pempty(b));
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[c0 + j] += __uint_as_float(v[j]);
+        }
+      }
+      if (!ok) break;
+      int w0, h0, n0, oc0, chunk0;
+      decode(t, w0, h0, n0, oc0, chunk0);
+      bool row_ok;
+      size_t pix;
+      if (p.linear) {
+        const long long px = (long long)(w0 / kTW) * BM + row;
+        row_ok = px < p.total_pixels;
+        pix = (size_t)px;
+      } else {
+        const int ow = w0 + gx, oh = h0 + ph, n = n0 + pn;
+        row_ok = pn < p.NB && ph < p.TH && ow < p.OW && oh < p.OH && n < p.N;
+        pix = ((size_t)n * p.OH + oh) * p.OW + ow;
+      }
+      row_ok = row_ok && !*abort_flag;
+      const int ocb = oc0 + half * NC;
+      float *o = p.out + pix * p.OC + ocb;
+#pragma unroll
+      for (int j = 0; j < NC; ++j) acc[j] *= p.out_scale;
+      if (vec && ocb + NC <= p.OC && small_out) {
+        // Coalesced path: a thread holds 32..64 channels of ONE pixel; through a 4 KiB staging
+        // block per warp the rows are turned so that eight lanes write one pixel's 128
+        // contiguous bytes (4 passes through the memory pipe per store instead of 32).
+        float4 *stage = reinterpret_cast<float4 *>(store_base + (warp - 8) * 4096);
+        const uint32_t off16 = row_ok ? (uint32_t)((o - p.out) >> 2) : 0xFFFFFFFFu;
+#pragma unroll
+        for (int h = 0; h < NC / 32; ++h) {
+#pragma unroll
+          for (int qq = 0; qq < 8; ++qq)  // 16-byte piece qq of row `lane` sits at piece qq ^ (lane & 7)
+            stage[lane * 8 + (qq ^ (lane & 7))] = make_float4(acc[h * 32 + 4 * qq], acc[h * 32 + 4 * qq + 1],
+                                                               acc[h * 32 + 4 * qq + 2], acc[h * 32 + 4 * qq + 3]);
+          __syncwarp();
+          float4 v[8];
+          const int qq = lane & 7;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + (lane >> 3);
+            v[i] = stage[r * 8 + (qq ^ (r & 7))];
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t off = __shfl_sync(0xffffffffu, off16, 4 * i + (lane >> 3));
+            float *dst = p.out + ((size_t)off << 2) + h * 32 + 4 * qq;
+            if (off != 0xFFFFFFFFu) {
+              if (p.ksplit > 1)  // a slice of the K range: add into the zeroed output
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v[i].x), "f"(v[i].y), "f"(v[i].z), "f"(v[i].w) : "memory");
+              else
+                *reinterpret_cast<float4 *>(dst) = v[i];
+            }
+          }
+          __syncwarp();
+        }
+        continue;
+      }
+      if (!row_ok) continue;
+      if (p.ksplit > 1) {
+#pragma unroll
+        for (int j = 0; j < NC; ++j)
+          if (ocb + j < p.OC) atomicAdd(o + j, acc[j]);
+      } else if (vec && ocb + NC <= p.OC) {
+#pragma unroll
+        for (int j = 0; j < NC; j += 4) *reinterpret_cast<float4 *>(o + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < NC; ++j)
+          if (ocb + j < p.OC) o[j] = acc[j];
+      }
+    }
+  }
+  if (warp == 8) PROF_OUT(5);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (tid == 0 && *abort_flag) atomicExch(p.error_flag, 1);
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
+// max |w| over the dense filter, as the bit pattern of a non-negative float (monotone in the value)
+__global__ void absmax_kernel(const float *__restrict__ w, size_t n, unsigned *out) {
+  unsigned m = 0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const unsigned b = __float_as_uint(w[i]) & 0x7FFFFFFFu;
+    if (b < 0x7F800000u) m = max(m, b);
+  }
+  for (int d = 16; d; d >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, d));
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+}
+
+// Dense OIHW -> the images the weight loader copies: for every (32-channel chunk, tap, channel
+// tile) BN rows of 128 bytes, row = output channel = {w_hi[32], w_lo[32]} FP16 of w * scale, in
+// the 128-byte-swizzled order the tensor core reads (16-byte piece j of row r sits at piece
+// j ^ (r & 7)).  Channels past IC or OC are zero.
+__global__ void tc16_weight_tiles_kernel(const float *__restrict__ filt, __half *__restrict__ tiles,
+                                         int OC, int IC, int KS, int n_chunks, int oc_tiles, int BN, float scale) {
+  const long long total = (long long)KS * KS * n_chunks * oc_tiles * BN * 64;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int col = (int)(i % 64);                 // FP16 position inside the stored row
+    const int row = (int)((i / 64) % BN);
+    long long tile = i / ((long long)64 * BN);     // images are stored [channel tile][chunk][tap]: the K steps of
+    const int tap = (int)(tile % (KS * KS));       // a work item lie back to back
+    tile /= KS * KS;
+    const int chunk = (int)(tile % n_chunks);
+    const int oct = (int)(tile / n_chunks);
+    const int piece = (col >> 3) ^ (row & 7);      // logical 16-byte piece stored at this position
+    const int k = ((piece & 3) << 3) | (col & 7);  // channel inside the chunk
+    const bool is_lo = piece >= 4;
+    const int oc = oct * BN + row, ic = chunk * KC + k;
+    float w = 0.f;
+    if (ic < IC && oc < OC) w = filt[((size_t)oc * IC + ic) * KS * KS + tap] * scale;
+    const __half h = __float2half_rn(w);
+    tiles[i] = is_lo ? __float2half_rn(w - __half2float(h)) : h;
+  }
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                             const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess) fn = (EncodeFn)p;
+  });
+  return fn;
+}
+
+struct Tc16State {
+  __half *d_tiles = nullptr;
+  int *d_error = nullptr;
+  unsigned *d_gate = nullptr;
+  int n_chunks = 0, bn = 128;
+  float out_scale = 1.f;
+  struct Setup {
+    bool valid = false;
+    const float *in = nullptr;
+    ConvShape shape{};
+    CUtensorMap map_x;
+    Tc16Params params{};
+    dim3 grid;
+    size_t smem = 0;
+  };
+  static constexpr int kSetups = 8;
+  std::mutex mutex;
+  Setup setups[kSetups];
+  int next_setup = 0;
+};
+
+constexpr size_t kSmemBudget = 227 * 1024;
+
+}  // namespace
+
+void conv_tc16_state_delete(void *state) {
+  Tc16State *s = static_cast<Tc16State *>(state);
+  if (!s) return;
+  cudaFree(s->d_tiles); cudaFree(s->d_error); cudaFree(s->d_gate);
+  delete s;
+}
+
+// Builds the split FP16 weight images (called from filter creation and from the file loader;
+// d_dense is the OIHW filter on the device).  Failure here is not fatal for the filter: the
+// variant is then reported as unsupported.
+int conv_tc16_prepare(tetris_filter *f, const float *d_dense) {
+  if (f->groups != 1 || (f->in_channel & 3) != 0 || f->in_channel < 8 || f->kernel_size > 7) return TETRIS_OK;
+  Tc16State *s = new (std::nothrow) Tc16State();
+  if (!s) return TETRIS_OK;
+  const int KS = f->kernel_size, taps = KS * KS;
+  s->n_chunks = (f->in_channel + KC - 1) / KC;
+  s->bn = f->out_channel <= 64 ? 64 : 128;
+  const int oc_tiles = (f->out_channel + s->bn - 1) / s->bn;
+  const size_t elems = (size_t)taps * s->n_chunks * oc_tiles * s->bn * 64;
+  const size_t n_dense = (size_t)f->out_channel * f->in_channel * taps;
+  if (cudaMalloc(&s->d_tiles, elems * sizeof(__half)) != cudaSuccess || cudaMalloc(&s->d_error, sizeof(int)) != cudaSuccess ||
+      cudaMalloc(&s->d_gate, 2 * sizeof(unsigned)) != cudaSuccess) {
+    cudaGetLastError();
+    conv_tc16_state_delete(s);
+    return TETRIS_OK;
+  }
+  cudaMemset(s->d_error, 0, sizeof(int));
+  cudaMemset(s->d_gate, 0, 2 * sizeof(unsigned));
+  // scale: the largest |w| lands in [2^12, 2^13]
+  unsigned bits = 0;
+  absmax_kernel<<<(unsigned)std::min<size_t>((n_dense + 255) / 256, 1024), 256>>>(d_dense, n_dense, s->d_gate);
+  if (cudaMemcpy(&bits, s->d_gate, sizeof(bits), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    cudaGetLastError();
+    conv_tc16_state_delete(s);
+    return TETRIS_OK;
+  }
+  cudaMemset(s->d_gate, 0, 2 * sizeof(unsigned));
+  float wmax;
+  memcpy(&wmax, &bits, sizeof(wmax));
+  int sh = 0;
+  if (wmax > 0.f) {
+    int e = 0;
+    std::frexp(wmax, &e);  // wmax = m * 2^e, m in [0.5, 1)
+    sh = 13 - e;
+    sh = std::max(-100, std::min(100, sh));
+  }
+  const float scale = std::ldexp(1.0f, sh);
+  s->out_scale = std::ldexp(1.0f, -sh) / kXScale;
+  tc16_weight_tiles_kernel<<<(unsigned)std::min<size_t>((elems + 255) / 256, 4096), 256>>>(
+      d_dense, s->d_tiles, f->out_channel, f->in_channel, KS, s->n_chunks, oc_tiles, s->bn, scale);
+  if (cudaGetLastError() != cudaSuccess) {
+    conv_tc16_state_delete(s);
+    return TETRIS_OK;
+  }
+  f->tc16_state = s;
+  return TETRIS_OK;
+}
+
+bool conv_tc16_supported(const tetris_filter *f, const ConvShape &s) {
+  if (!f->tc16_state || !f->tc_state || f->groups != 1) return false;  // (the split-TF32 variant is the out-of-range fallback)
+  if (s.S != 1 || s.N < 1 || s.OH < 1 || s.OW < 1 || (s.IC & 3) != 0) return false;
+  return conv_tc_supported(f, s);
+}
+
+int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const ConvShape &s, cudaStream_t st) {
+  Tc16State *t = static_cast<Tc16State *>(f->tc16_state);
+  if (!conv_tc16_supported(f, s) || (reinterpret_cast<uintptr_t>(in) & 15) != 0) {
+    set_error("split-FP16 tensor-core variant covers stride 1, in_channel a multiple of 4 (at least 8), 16-byte aligned inputs");
+    return TETRIS_ERR_UNSUPPORTED;
+  }
+  EncodeFn enc = get_encode();
+  if (!enc) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return TETRIS_ERR_UNSUPPORTED; }
+  CUtensorMap map_x;
+  Tc16Params p;
+  dim3 grid;
+  size_t smem = 0;
+  int bn = 128;
+  {
+    std::lock_guard<std::mutex> lock(t->mutex);
+    Tc16State::Setup *su = nullptr;
+    for (Tc16State::Setup &c : t->setups) {
+      const ConvShape &l = c.shape;
+      if (c.valid && c.in == in && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S) { su = &c; break; }
+    }
+    if (!su) {
+      su = &t->setups[t->next_setup];
+      t->next_setup = (t->next_setup + 1) % Tc16State::kSetups;
+      su->valid = false;
+      Tc16Params &q = su->params;
+      q = Tc16Params{};
+      const int KS = s.KS, halo = KS - 1;
+      q.N = s.N; q.OH = s.OH; q.OW = s.OW; q.OC = s.OC; q.P = s.P; q.KS = KS;
+      q.linear = (KS == 1 && s.P == 0) ? 1 : 0;
+      q.total_pixels = (long long)s.N * s.OH * s.OW;
+      cuuint64_t dims[4], strides[3];
+      cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+      if (q.linear) {
+        q.PW = kTW; q.PHI = kTH; q.TH = kTH; q.NB = 1;
+        q.box_rows = BM;
+        q.tiles_w = (int)((q.total_pixels + BM - 1) / BM); q.tiles_h = 1; q.tiles_n = 1;
+        dims[0] = (cuuint64_t)s.IC; dims[1] = (cuuint64_t)q.total_pixels; dims[2] = 1; dims[3] = 1;
+        strides[0] = (cuuint64_t)s.IC * 4; strides[1] = strides[0] * dims[1]; strides[2] = strides[1];
+        box[0] = KC; box[1] = BM; box[2] = 1; box[3] = 1;
+      } else {
+        q.PW = kTW + halo;
+        const bool whole = s.OH <= kTH;                 // the image's rows fit one tile
+        q.TH = whole ? s.OH : kTH;
+        q.PHI = q.TH + halo;
+        q.NB = whole ? std::max(1, std::min(s.N, (kTH + halo) / q.PHI)) : 1;
+        while (q.NB > 1 && (q.NB - 1) * q.PHI + q.TH > kTH) --q.NB;  // every valid group index stays below 16
+        q.box_rows = q.PW * q.PHI * q.NB;
+        q.tiles_w = (s.OW + kTW - 1) / kTW;
+        q.tiles_h = (s.OH + q.TH - 1) / q.TH;
+        q.tiles_n = (s.N + q.NB - 1) / q.NB;
+        dims[0] = (cuuint64_t)s.IC; dims[1] = (cuuint64_t)s.W; dims[2] = (cuuint64_t)s.H; dims[3] = (cuuint64_t)s.N;
+        strides[0] = (cuuint64_t)s.IC * 4; strides[1] = strides[0] * s.W; strides[2] = strides[1] * s.H;
+        box[0] = KC; box[1] = (cuuint32_t)q.PW; box[2] = (cuuint32_t)q.PHI; box[3] = (cuuint32_t)q.NB;
+      }
+      const CUresult r = enc(&su->map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(in), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return TETRIS_ERR_CUDA; }
+      // a stage holds the patch and whatever the windows of the 16 groups reach beyond it
+      const int reach_rows = q.linear ? BM : (kTH + halo) * q.PW + halo + 8;
+      q.x_stage_bytes = (std::max(reach_rows, q.box_rows) * 128 + 1023) / 1024 * 1024;
+      q.n_chunks = t->n_chunks;
+      q.w_tiles = t->d_tiles;
+      q.error_flag = t->d_error;
+      q.gate = t->d_gate;
+      q.out_scale = t->out_scale;
+      int dev = 0, sms = 0;
+      TETRIS_CUDA_TRY(cudaGetDevice(&dev));
+      TETRIS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      const long long tiles = (long long)q.tiles_w * q.tiles_h * q.tiles_n * ((s.OC + t->bn - 1) / t->bn);
+      // K range split into d work items per tile when that fills the waves of CTAs better (as in the
+      // split-TF32 variant; cost in K steps: waves x (K steps + ~12 per item) + zeroing the output)
+      const double iters = (double)KS * KS * q.n_chunks;
+      const double zeroing = ((double)s.N * s.OH * s.OW * s.OC * 4 / 6.0e12 + 3e-6) * 1.9e9 / 500.0;
+      int best_d = 1;
+      double best_cost = std::ceil((double)tiles / sms) * (iters + 12.0);
+      for (int d = 2; d <= 8 && d <= q.n_chunks && !f->deterministic; ++d) {
+        if (q.n_chunks % d) continue;
+        const double cost = std::ceil((double)tiles * d / sms) * (iters / d + 12.0) + zeroing;
+        if (cost < 0.96 * best_cost) { best_cost = cost; best_d = d; }
+      }
+      q.ksplit = best_d;
+      // shared memory: activation ring, weight ring, store staging, barriers
+      const size_t wbytes = (size_t)t->bn * 128 * 2;  // a weight stage holds a pair of K steps
+      const size_t fixed = 1024 + kStoreBytes + kNumBars * 8 + 16;
+      const int chunks_per_item = q.n_chunks / best_d;
+      q.n_w = kWStagesMax;
+      q.n_x = (int)std::min<size_t>(kXStagesMax, (kSmemBudget - fixed - q.n_w * wbytes) / q.x_stage_bytes);
+      while (q.n_x < 3 && q.n_w > 3) {  // (a pair of K steps may straddle two patches: at least two stages, better three)
+        --q.n_w;
+        q.n_x = (int)std::min<size_t>(kXStagesMax, (kSmemBudget - fixed - q.n_w * wbytes) / q.x_stage_bytes);
+      }
+      if (const char *e = getenv("TETRIS_TC16_NW")) q.n_w = std::max(2, std::min(kWStagesMax, atoi(e)));
+      if (const char *e = getenv("TETRIS_TC16_NW")) q.n_x = (int)std::min<size_t>(kXStagesMax, (kSmemBudget - fixed - q.n_w * wbytes) / q.x_stage_bytes);
+      if (q.n_x < 2) { set_error("split-FP16 variant: the activation patches of this layer do not fit shared memory"); return TETRIS_ERR_UNSUPPORTED; }
+      if (KS > 1) q.n_x = std::min(q.n_x, 3);          // a patch feeds KS*KS steps: three stages are ample
+      q.n_x = std::max(2, std::min(q.n_x, std::max(2, chunks_per_item)));
+      su->smem = fixed + (size_t)q.n_x * q.x_stage_bytes + (size_t)q.n_w * wbytes;
+      su->grid = dim3((unsigned)std::min<long long>(tiles * best_d, sms));  // persistent: one CTA per SM
+      su->in = in;
+      su->shape = s;
+      su->valid = true;
+    }
+    map_x = su->map_x;
+    p = su->params;
+    grid = su->grid;
+    smem = su->smem;
+    bn = t->bn;
+  }
+  p.out = out;
+  static long long *d_prof = nullptr;
+  const bool prof = getenv("TETRIS_TC16_PROF") != nullptr;
+  if (prof) {
+    if (!d_prof) cudaMalloc(&d_prof, 64 * sizeof(long long));
+    cudaMemset(d_prof, 0, 64 * sizeof(long long));
+    p.prof = d_prof;
+  }
+  if (const char *e = getenv("TETRIS_TC16_DBG")) p.dbg = atoi(e);
+  static thread_local bool configured[16] = {false};
+  int dev = 0;
+  TETRIS_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 16 || !configured[dev]) {
+    TETRIS_CUDA_TRY(cudaFuncSetAttribute(conv_tc16_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    TETRIS_CUDA_TRY(cudaFuncSetAttribute(conv_tc16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    if (dev < 16) configured[dev] = true;
+  }
+  if (p.ksplit > 1)  // the work items add into the output
+    TETRIS_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)s.N * s.OH * s.OW * s.OC * sizeof(float), st));
+  if (bn == 64)
+    conv_tc16_kernel<64><<<grid, kThreads, smem, st>>>(map_x, p);
+  else
+    conv_tc16_kernel<128><<<grid, kThreads, smem, st>>>(map_x, p);
+  TETRIS_CUDA_TRY(cudaGetLastError());
+  count_launch();
+  if (prof) {
+    long long h[64];
+    cudaDeviceSynchronize();
+    cudaMemcpy(h, d_prof, sizeof(h), cudaMemcpyDeviceToHost);
+    const char *names[6] = {"x loader (xempty)", "w loader (gdone)", "cp (gdone-4, xconv)", "mma (afull, pempty, wfull; mmas, commit)", "convert (xfull)", "sum (gdone)"};
+    const long long items = ((long long)p.tiles_w * p.tiles_h * p.tiles_n * ((s.OC + bn - 1) / bn) * p.ksplit + grid.x - 1) / grid.x;
+    const long long steps = items * (long long)s.KS * s.KS * (p.n_chunks / p.ksplit);
+    fprintf(stderr, "[tc16 prof] grid %u, items/CTA %lld, K steps/CTA %lld, n_x %d n_w %d\n", grid.x, items, steps, p.n_x, p.n_w);
+    for (int r = 0; r < 6; ++r)
+      fprintf(stderr, "[tc16 prof] %-42s total %9lld clk (%5.0f per K step); waits: %lld %lld %lld %lld %lld\n", names[r], h[r * 8],
+              (double)h[r * 8] / (double)steps, h[r * 8 + 1], h[r * 8 + 2], h[r * 8 + 3], h[r * 8 + 4], h[r * 8 + 5]);
+  }
+  // The guard: the split-TF32 variant, queued behind; it returns at once unless the largest
+  // activation of this launch lies outside FP16's useful window, in which case it recomputes the layer.
+  return launch_conv_tc_gated(f, in, out, s, st, t->d_gate);
+}
+
+// 0 = no timeout seen so far, 1 = a bounded wait gave up in some launch (the flag is cleared).
+int conv_tc16_check_error(const tetris_filter *f) {
+  Tc16State *t = static_cast<Tc16State *>(f->tc16_state);
+  if (!t) return 0;
+  int flag = 0;
+  if (cudaMemcpy(&flag, t->d_error, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return 1;
+  if (flag) cudaMemset(t->d_error, 0, sizeof(int));
+  return flag;
+}
+
+}  // namespace tetris

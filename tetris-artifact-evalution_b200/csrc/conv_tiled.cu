@@ -290,7 +290,7 @@ struct Plan {
   bool valid = false;
   ConvShape shape{};
   int instance = 0;  // which kernel template instance
-  bool use_tc = false;  // automatic choice: the dense tensor-core variant is expected to be faster
+  int use_tc = 0;  // automatic choice: 0 list kernel, 1 split-TF32 tensor-core variant, 2 split-FP16 tensor-core variant
   TiledParams p{};
   dim3 grid;
   size_t smem_bytes = 0;
@@ -441,7 +441,9 @@ int make_plan(const tetris_filter *f, const ConvShape &s, Plan *plan) {
   // The list kernel's wavefront model counts issue slots only and comes out 1.2-1.75x below the
   // measured time (1.45x on the layers where the two kernels are close); the tensor-core figure
   // is a measured one.
-  plan->use_tc = conv_tc_supported(f, s) && tc_cost(f, s, sm_count) < 1.45 * cands[0].cost;
+  // (the split-FP16 variant runs the same contraction at roughly half the clocks per K step)
+  if (conv_tc16_supported(f, s) && 0.55 * tc_cost(f, s, sm_count) < 1.45 * cands[0].cost) plan->use_tc = 2;
+  else plan->use_tc = conv_tc_supported(f, s) && tc_cost(f, s, sm_count) < 1.45 * cands[0].cost ? 1 : 0;
   return TETRIS_OK;
 }
 
@@ -487,7 +489,7 @@ void tiled_plans_export(const tetris_filter *f, std::vector<int32_t> *out) {
   std::lock_guard<std::mutex> lock(cache->mutex);
   for (const Plan &t : cache->tuned) {
     const int32_t rec[kTunedInts] = {t.shape.N, t.shape.H, t.shape.W, t.shape.S, t.shape.P,
-                                     t.instance, t.p.NSEG, t.p.TH, t.use_tc ? 1 : 0};
+                                     t.instance, t.p.NSEG, t.p.TH, t.use_tc};
     out->insert(out->end(), rec, rec + kTunedInts);
   }
 }
@@ -516,7 +518,7 @@ void tiled_plans_import(const tetris_filter *f, const int32_t *plans, int n) {
     Plan plan;
     if (plan_cost(f, s, kInstances[inst], NSEG, TH, sm_count, kSmemLimit, &plan) < 0.0) continue;
     plan.instance = inst;
-    plan.use_tc = r[8] != 0 && conv_tc_supported(f, s);
+    plan.use_tc = r[8] == 2 && conv_tc16_supported(f, s) ? 2 : r[8] != 0 && conv_tc_supported(f, s) ? 1 : 0;
     std::lock_guard<std::mutex> lock(cache->mutex);
     if (cache->tuned.size() < 8) cache->tuned.push_back(plan);
   }
@@ -604,7 +606,25 @@ int tune_conv_tiled(const tetris_filter *f, const float *in, float *out, const C
       cudaEventElapsedTime(&ms, e0, e1);
       ms /= reps;
       if (debug) fprintf(stderr, "[tetris tune] tensor-core variant -> %.4f ms\n", ms);
-      if (ms < best) { best = ms; best_plan.use_tc = true; }
+      if (ms < best) { best = ms; best_plan.use_tc = 1; }
+    }
+  }
+  // ... and the split-FP16 variant (its launch includes the guard kernel queued behind it)
+  if (!rc && conv_tc16_supported(f, s) && (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
+    rc = launch_conv_tc16(f, in, out, s, st);
+    cudaEventRecord(e0, st);
+    for (int i = 0; i < reps && !rc; ++i) rc = launch_conv_tc16(f, in, out, s, st);
+    cudaEventRecord(e1, st);
+    if (!rc && cudaEventSynchronize(e1) != cudaSuccess) {
+      set_error("tuning launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+      rc = TETRIS_ERR_CUDA;
+    }
+    if (!rc && !conv_tc16_check_error(f)) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, e0, e1);
+      ms /= reps;
+      if (debug) fprintf(stderr, "[tetris tune] split-FP16 tensor-core variant -> %.4f ms\n", ms);
+      if (ms < best) { best = ms; best_plan.use_tc = 2; }
     }
   }
   cudaEventDestroy(e0);
@@ -641,7 +661,7 @@ int conv_auto_choice(const tetris_filter *f, const ConvShape &s, int *variant) {
     const int rc = make_plan(f, s, &plan);
     if (rc) return rc;
   }
-  *variant = plan.use_tc ? TETRIS_VARIANT_TENSOR : TETRIS_VARIANT_TILED;
+  *variant = plan.use_tc == 2 ? TETRIS_VARIANT_TENSOR16 : plan.use_tc ? TETRIS_VARIANT_TENSOR : TETRIS_VARIANT_TILED;
   return TETRIS_OK;
 }
 
@@ -672,7 +692,7 @@ int launch_conv_tiled(const tetris_filter *f, const float *in, float *out, const
     }
   }
   if (allow_tc && plan.use_tc && (reinterpret_cast<uintptr_t>(in) & 15) == 0)
-    return launch_conv_tc(f, in, out, s, st);
+    return plan.use_tc == 2 ? launch_conv_tc16(f, in, out, s, st) : launch_conv_tc(f, in, out, s, st);
   return launch_plan(plan, in, out, st);
 }
 

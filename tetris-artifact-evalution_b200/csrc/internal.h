@@ -28,6 +28,7 @@ struct tetris_filter {
   int deterministic;       // 1: the tensor-core variant never splits a tile's K range (no atomic adds)
   void *plan_cache;        // tiled kernel: launch plan of the last conv shape (conv_tiled.cu)
   void *tc_state;          // tensor-core variant: split dense weights + tensor maps (conv_tc.cu)
+  void *tc16_state;        // split-FP16 tensor-core variant: weight images + tensor maps (conv_tc16.cu)
 };
 
 namespace tetris {
@@ -89,6 +90,13 @@ bool conv_tc_supported(const tetris_filter *f, const ConvShape &s);
 int launch_conv_tc(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                    cudaStream_t st);
 int conv_tc_check_error(const tetris_filter *f);
+int launch_conv_tc_gated(const tetris_filter *f, const float *in, float *out, const ConvShape &s, cudaStream_t st,
+                         unsigned *gate);
+int conv_tc16_prepare(tetris_filter *f, const float *d_dense);
+void conv_tc16_state_delete(void *state);
+bool conv_tc16_supported(const tetris_filter *f, const ConvShape &s);
+int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const ConvShape &s, cudaStream_t st);
+int conv_tc16_check_error(const tetris_filter *f);
 int launch_depthwise(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                      cudaStream_t st);
 int launch_nchw_to_nhwc(const float *src, float *dst, int N, int C, int H, int W, cudaStream_t st);

@@ -261,7 +261,7 @@ int tetris_filter_load(const char *path, int device, tetris_filter_t **out) {
     const int P = f->n_oc_blocks * f->n_stages;
     lists_to_dense_kernel<<<(P + 7) / 8, 256>>>(f->d_lists, f->d_list_offsets, d_dense, f->in_channel, f->out_channel,
                                                  f->kernel_size, f->oc_block, f->tile_ic, f->n_oc_blocks, f->n_stages);
-    if ((rc = conv_tc_prepare(f, d_dense))) return fail(rc);
+    if ((rc = conv_tc_prepare(f, d_dense)) || (rc = conv_tc16_prepare(f, d_dense))) return fail(rc);
     if (cudaDeviceSynchronize() != cudaSuccess) {
       set_error("rebuilding the tensor-core tile images failed: %s", cudaGetErrorString(cudaGetLastError()));
       return fail(TETRIS_ERR_CUDA);
