@@ -3,11 +3,12 @@
 //
 // Arithmetic.  x = x_hi + x_lo and w' = w * 2^sh = w_hi + w_lo with *_hi the value rounded to
 // FP16 (11 significant bits) and *_lo the FP16-rounded remainder; D += x_hi*w_hi + x_lo*w_hi +
-// x_hi*w_lo in FP32 accumulators, scaled back by 2^-sh (exact) at the store.  The products are
+// x_hi*w_lo in FP32 accumulators, scaled back by 2^-sh (exact) at the store; sh is chosen per
+// OUTPUT CHANNEL, so channels of very different magnitude keep their own full precision.  The products are
 // exact in FP32; what is dropped is x_lo*w_lo and the rounding of the remainders, about 2^-22 of
 // a product each -- the same as the split-TF32 variant (conv_tc.cu), at twice the tensor-core
-// rate and half the operand bytes.  sh is chosen per filter so that the largest |w'| is about
-// 2^13: weights down to 2^-17 of the largest keep a normal FP16 remainder.  Activations are
+// rate and half the operand bytes.  sh puts a channel's largest |w'| at about 2^13: weights down
+// to 2^-17 of the channel's largest keep a normal FP16 remainder.  Activations are
 // scaled by a fixed 16 (their range is not known before the launch), which puts FP16's window at
 // |x| < 2048 with remainders exact down to |x| = 2^-7 and an absolute error of at most 2e-9 per
 // activation below that.  The conversion warps record the largest magnitude of the launch in
@@ -91,7 +92,7 @@ struct Tc16Params {
   int tiles_w, tiles_h, tiles_n;
   int n_chunks, ksplit;
   long long total_pixels;      // N * OH * OW (linear mode)
-  float out_scale;             // 2^-sh
+  const float *out_scale;      // per output channel: 2^-sh[oc] / 16 (undoes the weight and activation scaling)
   int *error_flag;
   unsigned *gate;              // gate[0]: largest |activation| of the launch, as FP32 bits (see launch_conv_tc_gated)
   const __half *w_tiles;
@@ -501,7 +502,7 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
       const int ocb = oc0 + half * NC;
       float *o = p.out + pix * p.OC + ocb;
 #pragma unroll
-      for (int j = 0; j < NC; ++j) acc[j] *= p.out_scale;
+      for (int j = 0; j < NC; ++j) acc[j] *= (ocb + j < p.OC) ? __ldg(p.out_scale + ocb + j) : 0.f;
       if (vec && ocb + NC <= p.OC && small_out) {
         // Coalesced path: a thread holds 32..64 channels of ONE pixel; through a 4 KiB staging
         // block per warp the rows are turned so that eight lanes write one pixel's 128
@@ -559,23 +560,38 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
   if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
-// max |w| over the dense filter, as the bit pattern of a non-negative float (monotone in the value)
-__global__ void absmax_kernel(const float *__restrict__ w, size_t n, unsigned *out) {
+// Per output channel: the power of two that brings the channel's largest |w| into [2^12, 2^13)
+// (1 for an all-zero channel), and its inverse divided by the activation scale.
+__global__ void tc16_scales_kernel(const float *__restrict__ w, int per_oc, float *__restrict__ w_scale, float *__restrict__ out_scale) {
+  const float *row = w + (size_t)blockIdx.x * per_oc;
   unsigned m = 0;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const unsigned b = __float_as_uint(w[i]) & 0x7FFFFFFFu;
+  for (int i = threadIdx.x; i < per_oc; i += blockDim.x) {
+    const unsigned b = __float_as_uint(row[i]) & 0x7FFFFFFFu;
     if (b < 0x7F800000u) m = max(m, b);
   }
+  __shared__ unsigned red[32];
   for (int d = 16; d; d >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, d));
-  if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) m = max(m, red[i]);
+    int sh = 0;
+    if (m) {
+      int e;
+      frexpf(__uint_as_float(m), &e);  // |w|max = f * 2^e, f in [0.5, 1)
+      sh = min(100, max(-100, 13 - e));
+    }
+    w_scale[blockIdx.x] = ldexpf(1.f, sh);
+    out_scale[blockIdx.x] = ldexpf(1.f, -sh) / kXScale;
+  }
 }
 
 // Dense OIHW -> the images the weight loader copies: for every (32-channel chunk, tap, channel
-// tile) BN rows of 128 bytes, row = output channel = {w_hi[32], w_lo[32]} FP16 of w * scale, in
+// tile) BN rows of 128 bytes, row = output channel = {w_hi[32], w_lo[32]} FP16 of w * scale[oc], in
 // the 128-byte-swizzled order the tensor core reads (16-byte piece j of row r sits at piece
 // j ^ (r & 7)).  Channels past IC or OC are zero.
 __global__ void tc16_weight_tiles_kernel(const float *__restrict__ filt, __half *__restrict__ tiles,
-                                         int OC, int IC, int KS, int n_chunks, int oc_tiles, int BN, float scale) {
+                                         int OC, int IC, int KS, int n_chunks, int oc_tiles, int BN, const float *__restrict__ scale) {
   const long long total = (long long)KS * KS * n_chunks * oc_tiles * BN * 64;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int col = (int)(i % 64);                 // FP16 position inside the stored row
@@ -590,7 +606,7 @@ __global__ void tc16_weight_tiles_kernel(const float *__restrict__ filt, __half 
     const bool is_lo = piece >= 4;
     const int oc = oct * BN + row, ic = chunk * KC + k;
     float w = 0.f;
-    if (ic < IC && oc < OC) w = filt[((size_t)oc * IC + ic) * KS * KS + tap] * scale;
+    if (ic < IC && oc < OC) w = filt[((size_t)oc * IC + ic) * KS * KS + tap] * scale[oc];
     const __half h = __float2half_rn(w);
     tiles[i] = is_lo ? __float2half_rn(w - __half2float(h)) : h;
   }
@@ -616,7 +632,7 @@ struct Tc16State {
   int *d_error = nullptr;
   unsigned *d_gate = nullptr;
   int n_chunks = 0, bn = 128;
-  float out_scale = 1.f;
+  float *d_out_scale = nullptr;  // per output channel
   struct Setup {
     bool valid = false;
     const float *in = nullptr;
@@ -639,7 +655,7 @@ constexpr size_t kSmemBudget = 227 * 1024;
 void conv_tc16_state_delete(void *state) {
   Tc16State *s = static_cast<Tc16State *>(state);
   if (!s) return;
-  cudaFree(s->d_tiles); cudaFree(s->d_error); cudaFree(s->d_gate);
+  cudaFree(s->d_tiles); cudaFree(s->d_error); cudaFree(s->d_gate); cudaFree(s->d_out_scale);
   delete s;
 }
 
@@ -655,7 +671,6 @@ int conv_tc16_prepare(tetris_filter *f, const float *d_dense) {
   s->bn = f->out_channel <= 64 ? 64 : 128;
   const int oc_tiles = (f->out_channel + s->bn - 1) / s->bn;
   const size_t elems = (size_t)taps * s->n_chunks * oc_tiles * s->bn * 64;
-  const size_t n_dense = (size_t)f->out_channel * f->in_channel * taps;
   if (cudaMalloc(&s->d_tiles, elems * sizeof(__half)) != cudaSuccess || cudaMalloc(&s->d_error, sizeof(int)) != cudaSuccess ||
       cudaMalloc(&s->d_gate, 2 * sizeof(unsigned)) != cudaSuccess) {
     cudaGetLastError();
@@ -664,29 +679,22 @@ int conv_tc16_prepare(tetris_filter *f, const float *d_dense) {
   }
   cudaMemset(s->d_error, 0, sizeof(int));
   cudaMemset(s->d_gate, 0, 2 * sizeof(unsigned));
-  // scale: the largest |w| lands in [2^12, 2^13]
-  unsigned bits = 0;
-  absmax_kernel<<<(unsigned)std::min<size_t>((n_dense + 255) / 256, 1024), 256>>>(d_dense, n_dense, s->d_gate);
-  if (cudaMemcpy(&bits, s->d_gate, sizeof(bits), cudaMemcpyDeviceToHost) != cudaSuccess) {
+  // per-channel scales: every output channel's largest |w| lands in [2^12, 2^13)
+  float *d_w_scale = nullptr;
+  if (cudaMalloc(&d_w_scale, f->out_channel * sizeof(float)) != cudaSuccess ||
+      cudaMalloc(&s->d_out_scale, f->out_channel * sizeof(float)) != cudaSuccess) {
     cudaGetLastError();
+    cudaFree(d_w_scale);
     conv_tc16_state_delete(s);
     return TETRIS_OK;
   }
-  cudaMemset(s->d_gate, 0, 2 * sizeof(unsigned));
-  float wmax;
-  memcpy(&wmax, &bits, sizeof(wmax));
-  int sh = 0;
-  if (wmax > 0.f) {
-    int e = 0;
-    std::frexp(wmax, &e);  // wmax = m * 2^e, m in [0.5, 1)
-    sh = 13 - e;
-    sh = std::max(-100, std::min(100, sh));
-  }
-  const float scale = std::ldexp(1.0f, sh);
-  s->out_scale = std::ldexp(1.0f, -sh) / kXScale;
+  tc16_scales_kernel<<<f->out_channel, 256>>>(d_dense, f->in_channel * taps, d_w_scale, s->d_out_scale);
   tc16_weight_tiles_kernel<<<(unsigned)std::min<size_t>((elems + 255) / 256, 4096), 256>>>(
-      d_dense, s->d_tiles, f->out_channel, f->in_channel, KS, s->n_chunks, oc_tiles, s->bn, scale);
-  if (cudaGetLastError() != cudaSuccess) {
+      d_dense, s->d_tiles, f->out_channel, f->in_channel, KS, s->n_chunks, oc_tiles, s->bn, d_w_scale);
+  const cudaError_t err = cudaGetLastError();
+  cudaStreamSynchronize(0);  // (d_w_scale is freed next)
+  cudaFree(d_w_scale);
+  if (err != cudaSuccess) {
     conv_tc16_state_delete(s);
     return TETRIS_OK;
   }
@@ -765,7 +773,7 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
       q.w_tiles = t->d_tiles;
       q.error_flag = t->d_error;
       q.gate = t->d_gate;
-      q.out_scale = t->out_scale;
+      q.out_scale = t->d_out_scale;
       int dev = 0, sms = 0;
       TETRIS_CUDA_TRY(cudaGetDevice(&dev));
       TETRIS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
