@@ -440,6 +440,26 @@ def main():
                     rec[name] = None
             arms.append(rec)
 
+    # ---- real pruned layers beside their uniform-mask twins (same shape, same nonzero values at
+    #      uniformly random positions): what the skew of magnitude-pruned rows costs each kernel ----
+    skew = None
+    if args.workload == "real" and world == 1:
+        skew = []
+        for l in layers:
+            L = l["L"]
+            twin = tb.SparseFilter(wl.uniform_like(l["filt"], seed=7), L.IC, L.OC, L.KS, device=local)
+            rows = np.count_nonzero(l["filt"].reshape(L.OC, -1), axis=1)
+            rec = {"name": L.name, "row_nnz_min_mean_max": [int(rows.min()), float(rows.mean()), int(rows.max())],
+                   "empty_rows": int((rows == 0).sum())}
+            for key, v in (("tiled", tb.VARIANT_TILED), ("auto", tb.VARIANT_AUTO)):
+                if v == tb.VARIANT_AUTO:
+                    tb.tune_sparse_conv2d(twin, l["x"], l["y"], batch, L.H, L.W, L.stride, L.pad, cuda_stream=stream)
+                a = tb.timing_sparse_conv2d(l["f"], l["x"], l["y"], batch, L.H, L.W, L.stride, L.pad, variant=v, warm=3, repeat=10)
+                b = tb.timing_sparse_conv2d(twin, l["x"], l["y"], batch, L.H, L.W, L.stride, L.pad, variant=v, warm=3, repeat=10)
+                rec[key + "_real_ms"], rec[key + "_uniform_ms"], rec[key + "_skew_penalty"] = a, b, a / b - 1.0
+            skew.append(rec)
+            twin.close()
+
     # ---- sustained: the step looped for seconds, with the clocks and the power seen ----
     sustained = None
     if args.sustained_s > 0 and world == 1:
@@ -703,7 +723,7 @@ def main():
         "step_ms_min_max": [min(step_ms), max(step_ms)],
         "timed_as": "CUDA-graph replay of the step's launches", "eager": eager_info, "sustained": sustained, "strong": strong, "sharded_one_process": sharded,
         "cudnn_context": cudnn, "cudnn_ms_per_step": cudnn["ms_per_step"] if cudnn else None,
-        "workloads": workloads_block,
+        "workloads": workloads_block, "real_vs_uniform": skew,
         "per_layer": per_layer,
     }))
     if world > 1:

@@ -124,7 +124,7 @@ def load_real_layer(path):
     dense = np.zeros(oc * ic * ks * ks, np.float32)
     dense[z["index"]] = z["value"]
     name = os.path.basename(path)[:-4]
-    short = name.split("__")[0] + "_" + "_".join(name.split("_H_")[1].split("_")[i] for i in (0, 3, 5, 7, 11))
+    short = "%s_%dx%d_%dto%d_k%ds%d" % (name.split("__")[0], h, w, ic, oc, ks, stride)
     sparsity = 1.0 - z["index"].size / dense.size
     # the reference reads the groups field and ignores it (Tetris/tensor_utils.cc:66)
     return Layer(short, h, w, ic, oc, ks, pad, stride, 1, sparsity), dense.reshape(oc, ic, ks, ks)
