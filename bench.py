@@ -123,7 +123,8 @@ class Model:
         for idx, L in enumerate(wl.WORKLOADS[workload]()):
             filt = wl.make_filter(workload, idx, L)
             path = os.path.join(plan_cache, "%s_%02d_%s.tetris" % (workload, idx, L.name)) if plan_cache else None
-            if path and os.path.exists(path):
+            loaded = bool(path and os.path.exists(path))
+            if loaded:
                 f = tb.SparseFilter.load(path, device=device)   # compressed forms + tuned tile plans
             else:
                 f = tb.SparseFilter(filt, L.IC, L.OC, L.KS, TILE_IC=tile_ic, groups=L.groups, device=device,
@@ -134,7 +135,7 @@ class Model:
             x = x * (torch.rand(x.shape, device="cuda", generator=g) >= 0.5)
             y = torch.empty(max_batch, oh, ow, L.OC, device="cuda")
             self.layers.append(dict(L=L, f=f, x=x, y=y, oh=oh, ow=ow, nnz=int(f.nnz_), filt=filt,
-                                    variant=variant, path=path))
+                                    variant=variant, path=path, loaded=loaded))
 
     def costs(self, batch):
         return [self.wl.layer_costs(l["L"], batch, l["nnz"]) for l in self.layers]
@@ -161,7 +162,7 @@ class Model:
             return
         for l in self.layers:
             L = l["L"]
-            if l["variant"] == 0:
+            if l["variant"] == 0 and not l["loaded"]:   # (a filter from the plan cache brings its tuned plans along)
                 self.tb.tune_sparse_conv2d(l["f"], l["x"], l["y"], batch, L.H, L.W, L.stride, L.pad,
                                            cuda_stream=stream)
                 if l["path"]:

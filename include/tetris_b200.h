@@ -148,6 +148,50 @@ int tetris_conv2d_launch_ex(const tetris_filter_t *f, const float *d_input_nhwc,
                             int stride, int padding, void *stream, int variant);
 
 /*
+ * The same launch with options fused into the kernel's store.  flags: TETRIS_FUSE_RELU -- the
+ * output is max(y, 0).  The tensor-core variants rectify at their own store (and do not split a
+ * tile's K range for such a launch); the other kernels are followed by an in-place pass on the
+ * same stream.  No counterpart in the reference, whose kernel writes the plain convolution
+ * (Tetris/spconv2d_kernel.cu:140-158).
+ */
+enum { TETRIS_FUSE_RELU = 1 };
+int tetris_conv2d_launch_fused(const tetris_filter_t *f, const float *d_input_nhwc, float *d_output_nhwc,
+                               int batch_size, int img_h, int img_w, int stride, int padding, void *stream,
+                               int variant, int flags);
+
+/*
+ * Layer chains: the convolutions of a model run back to back on the device.  Layer i reads what
+ * layer i - 1 left in HBM (NHWC), optionally rectified (relu) and 2x2 max-pooled (pool = 2; 0 =
+ * none); the chain owns the activation buffers between the layers.  The reference has no chained
+ * execution: it times isolated layers and adds the times up per model
+ * (evalution/overall_speedup.py:159-165).
+ *   tetris_chain_create   checks that the layers fit together (channels, extents) and allocates
+ *                         the activations for `batch_size` images of img_h x img_w; all filters
+ *                         must live on one device.  The filters stay the caller's.
+ *   tetris_chain_run      queues every launch on `stream` (asynchronous, allocates nothing).
+ *   tetris_chain_capture  runs the chain once, then captures it into a CUDA graph for this input
+ *                         pointer; tetris_chain_replay launches that graph on `stream`.
+ *   tetris_chain_output   the last layer's output (device pointer owned by the chain) and extent.
+ *   tetris_chain_download waits for the device and copies that output (NHWC) to the host;
+ *                         `capacity` in floats.
+ */
+typedef struct tetris_chain tetris_chain_t;
+typedef struct {
+  const tetris_filter_t *filter;
+  int stride, padding;
+  int relu;  /* 1: max(y, 0) after the convolution                       */
+  int pool;  /* 2: 2x2 max-pooling, stride 2, after that; 0: none        */
+} tetris_chain_layer_t;
+int tetris_chain_create(const tetris_chain_layer_t *layers, int n_layers, int batch_size, int img_h, int img_w,
+                        tetris_chain_t **out);
+void tetris_chain_destroy(tetris_chain_t *c);
+int tetris_chain_run(tetris_chain_t *c, const float *d_input_nhwc, void *stream);
+int tetris_chain_capture(tetris_chain_t *c, const float *d_input_nhwc);
+int tetris_chain_replay(tetris_chain_t *c, void *stream);
+int tetris_chain_output(const tetris_chain_t *c, const float **d_output_nhwc, int *h, int *w, int *channels);
+int tetris_chain_download(const tetris_chain_t *c, float *h_output_nhwc, size_t capacity);
+
+/*
  * The reference's timing protocol: `warm` untimed launches, a device
  * synchronise, then `repeat` back-to-back launches between two events on
  * `stream`; *ms_mean = elapsed / repeat.

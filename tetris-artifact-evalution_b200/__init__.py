@@ -67,6 +67,14 @@ SIGNATURES = {
     "tetris_filter_check": (_I, [_VP]),
     "tetris_conv2d_launch": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
     "tetris_conv2d_launch_ex": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I]),
+    "tetris_conv2d_launch_fused": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _I]),
+    "tetris_chain_create": (_I, [_VP, _I, _I, _I, _I, ctypes.POINTER(_VP)]),
+    "tetris_chain_destroy": (None, [_VP]),
+    "tetris_chain_run": (_I, [_VP, _VP, _VP]),
+    "tetris_chain_capture": (_I, [_VP, _VP]),
+    "tetris_chain_replay": (_I, [_VP, _VP]),
+    "tetris_chain_download": (_I, [_VP, _VP, ctypes.c_size_t]),
+    "tetris_chain_output": (_I, [_VP, ctypes.POINTER(_VP), _c_int_p, _c_int_p, _c_int_p]),
     "tetris_conv2d_time": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _I, _I, _c_float_p]),
     "tetris_conv2d_tune": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _c_float_p]),
     "tetris_conv2d_choice": (_I, [_VP, _I, _I, _I, _I, _I, _c_int_p]),
@@ -245,6 +253,70 @@ def sparse_conv2d(sparse_filter, input, output, batch_size, img_h, img_w, stride
     _check(lib().tetris_conv2d_launch_ex(sparse_filter.handle, _ptr(input), _ptr(output), batch_size,
                                          img_h, img_w, stride, padding, _stream_ptr(cuda_stream),
                                          variant))
+
+
+FUSE_RELU = 1
+
+
+def sparse_conv2d_fused(sparse_filter, input, output, batch_size, img_h, img_w, stride, padding,
+                        cuda_stream=None, variant=VARIANT_AUTO, relu=True):
+    """sparse_conv2d with max(y, 0) applied at the store (tetris_conv2d_launch_fused)."""
+    _check(lib().tetris_conv2d_launch_fused(sparse_filter.handle, _ptr(input), _ptr(output), batch_size,
+                                            img_h, img_w, stride, padding, _stream_ptr(cuda_stream),
+                                            variant, FUSE_RELU if relu else 0))
+
+
+class ChainLayer(ctypes.Structure):
+    _fields_ = [("filter", _VP), ("stride", _I), ("padding", _I), ("relu", _I), ("pool", _I)]
+
+
+class LayerChain:
+    """The conv layers of a model run back to back on the device (tetris_chain_*).
+
+    `layers` is a list of (SparseFilter, stride, padding, relu, pool) with pool in (0, 2).  The
+    chain owns the activations between the layers; the filters stay the caller's and must
+    outlive the chain.
+    """
+
+    def __init__(self, layers, batch_size, img_h, img_w):
+        self._filters = [l[0] for l in layers]
+        arr = (ChainLayer * len(layers))(*[ChainLayer(l[0].handle, l[1], l[2], 1 if l[3] else 0, l[4]) for l in layers])
+        self._handle = _VP()
+        _check(lib().tetris_chain_create(arr, len(layers), batch_size, img_h, img_w, ctypes.byref(self._handle)))
+        self.batch = batch_size
+
+    def run(self, input, cuda_stream=None):
+        _check(lib().tetris_chain_run(self._handle, _ptr(input), _stream_ptr(cuda_stream)))
+
+    def capture(self, input):
+        _check(lib().tetris_chain_capture(self._handle, _ptr(input)))
+
+    def replay(self, cuda_stream=None):
+        _check(lib().tetris_chain_replay(self._handle, _stream_ptr(cuda_stream)))
+
+    def output(self):
+        """(device address, h, w, channels) of the last layer's output."""
+        p, h, w, c = _VP(), _I(), _I(), _I()
+        _check(lib().tetris_chain_output(self._handle, ctypes.byref(p), ctypes.byref(h), ctypes.byref(w), ctypes.byref(c)))
+        return p.value, h.value, w.value, c.value
+
+    def download(self):
+        """The last layer's output as a host NHWC float32 array (waits for the device)."""
+        _, h, w, c = self.output()
+        host = np.empty((self.batch, h, w, c), np.float32)
+        _check(lib().tetris_chain_download(self._handle, host.ctypes.data, host.size))
+        return host
+
+    def close(self):
+        if getattr(self, "_handle", None):
+            lib().tetris_chain_destroy(self._handle)
+            self._handle = _VP()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def timing_sparse_conv2d(sparse_filter, input, output, batch_size, img_h, img_w, stride, padding,

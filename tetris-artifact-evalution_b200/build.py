@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtetris_b200.so")
 SOURCES = ["api.cu", "compress.cu", "conv_generic.cu", "conv_tiled.cu", "conv_tc.cu", "conv_tc16.cu", "depthwise.cu", "layout.cu",
-           "noalloc.cu", "serialize.cu"]
+           "noalloc.cu", "serialize.cu", "chain.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-shared", "-Xcompiler", "-fPIC",

@@ -71,8 +71,23 @@ int make_shape(const tetris_filter *f, int batch, int h, int w, int stride, int 
   return TETRIS_OK;
 }
 
+thread_local bool tl_relu_fused = false;
+
+int dispatch_kernel(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
+                    cudaStream_t st, int variant);
+
+// One convolution launch.  A requested ReLU is applied at the kernel's own store where the
+// kernel can do that (the tensor-core variants), else by an in-place pass behind it.
 int dispatch(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
              cudaStream_t st, int variant) {
+  tl_relu_fused = false;
+  const int rc = dispatch_kernel(f, in, out, s, st, variant);
+  if (rc || !s.relu || tl_relu_fused || s.N == 0) return rc;
+  return launch_relu_inplace(out, (size_t)s.N * s.OH * s.OW * s.OC, st);
+}
+
+int dispatch_kernel(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
+                    cudaStream_t st, int variant) {
   if (s.N == 0) return TETRIS_OK;
   if (f->groups != 1) return launch_depthwise(f, in, out, s, st);
   switch (variant) {
@@ -97,6 +112,13 @@ int dispatch(const tetris_filter *f, const float *in, float *out, const ConvShap
 }
 
 }  // namespace
+
+void note_relu_fused() { tl_relu_fused = true; }
+
+int conv_dispatch_auto(const tetris_filter *f, const float *in, float *out, const ConvShape &s, cudaStream_t st) {
+  return dispatch(f, in, out, s, st, TETRIS_VARIANT_AUTO);
+}
+
 }  // namespace tetris
 
 using namespace tetris;
@@ -364,6 +386,18 @@ int tetris_conv2d_launch_ex(const tetris_filter_t *f, const float *d_input_nhwc,
     set_error("input or output pointer is NULL");
     return TETRIS_ERR_INVALID;
   }
+  return dispatch(f, d_input_nhwc, d_output_nhwc, s, (cudaStream_t)stream, variant);
+}
+
+int tetris_conv2d_launch_fused(const tetris_filter_t *f, const float *d_input_nhwc, float *d_output_nhwc,
+                               int batch_size, int img_h, int img_w, int stride, int padding, void *stream,
+                               int variant, int flags) {
+  ConvShape s;
+  int rc = make_shape(f, batch_size, img_h, img_w, stride, padding, &s);
+  if (rc) return rc;
+  if (batch_size > 0 && (!d_input_nhwc || !d_output_nhwc)) { set_error("input or output pointer is NULL"); return TETRIS_ERR_INVALID; }
+  if (flags & ~TETRIS_FUSE_RELU) { set_error("unknown fusion flags 0x%x", flags); return TETRIS_ERR_INVALID; }
+  s.relu = (flags & TETRIS_FUSE_RELU) ? 1 : 0;
   return dispatch(f, d_input_nhwc, d_output_nhwc, s, (cudaStream_t)stream, variant);
 }
 

@@ -113,6 +113,7 @@ struct TcParams {
   int tiles_w, tiles_h, tiles_n;
   int n_chunks;                // ceil(IC / 32)
   int ksplit;                  // work items per tile: each takes n_chunks / ksplit chunks and adds its result in
+  int relu;                    // max(y, 0) at the store (never together with a split K range)
   int *error_flag;
   const float *w_tiles;        // weight tile images, see tc_weight_tiles_kernel
   unsigned *gate;              // when set: the launch runs only if the magnitude in gate[0] asks for it (see launch_conv_tc_gated)
@@ -595,6 +596,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         }
       }
       if (!ok) break;
+      if (p.relu) {
+#pragma unroll
+        for (int j = 0; j < NC; ++j) acc[j] = fmaxf(acc[j], 0.f);
+      }
       // the item's tile coordinates, counted along in mixed radix (see `step` below)
       const int w0 = cur[2] * p.TW, h0 = cur[3] * p.TH, n0 = cur[4] * p.NB, oc0 = cur[1] * BN;
       {
@@ -847,7 +852,7 @@ int launch_conv_tc_impl(const tetris_filter *f, const float *in, float *out, con
     TcState::Setup *su = nullptr;
     for (TcState::Setup &c : t->setups) {
       const ConvShape &l = c.shape;
-      if (c.valid && c.in == in && c.gated == (gate != nullptr) && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S) { su = &c; break; }
+      if (c.valid && c.in == in && c.gated == (gate != nullptr) && l.relu == s.relu && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S) { su = &c; break; }
     }
     if (!su) {
       su = &t->setups[t->next_setup];
@@ -909,7 +914,8 @@ int launch_conv_tc_impl(const tetris_filter *f, const float *in, float *out, con
       const double zeroing = ((double)s.N * s.OH * s.OW * s.OC * 4 / 6.0e12 + 3e-6) * 1.9e9 / 1450.0;
       int best_d = 1;
       double best_cost = std::ceil((double)tiles / sms) * (iters + 10.0);
-      for (int d = 2; d <= 8 && d <= q.n_chunks && !f->deterministic && !gate; ++d) {
+      q.relu = s.relu;
+      for (int d = 2; d <= 8 && d <= q.n_chunks && !f->deterministic && !gate && !s.relu; ++d) {
         if (q.n_chunks % d) continue;
         const double cost = std::ceil((double)tiles * d / sms) * (iters / d + 10.0) + zeroing;
         if (cost < 0.96 * best_cost) { best_cost = cost; best_d = d; }
@@ -950,6 +956,7 @@ int launch_conv_tc_impl(const tetris_filter *f, const float *in, float *out, con
     conv_tc_kernel<128><<<grid, kThreads, smem, st>>>(map_x, p);
   TETRIS_CUDA_TRY(cudaGetLastError());
   if (!gate) count_launch();
+  if (p.relu) note_relu_fused();
   return TETRIS_OK;
 }
 }  // namespace

@@ -75,7 +75,7 @@ constexpr int kGroups = 16;              // "pair done" barriers in rotation (a 
 constexpr int kSuper = 4;                // pairs (8 K steps, 48 MMAs) accumulated on the tensor core before the FP32 add outside
 constexpr int kThreads = 512;            // warp 0 x loads, 1 MMA, 2 w loads, 3 cp, 4-7 convert, 8-15 sum + store
 constexpr int kStoreBytes = 8 * 4096;    // store staging: per summing warp 32 rows x 32 channels
-constexpr int kNumBars = 3 * kXStagesMax + kWStagesMax + 2 * kAStages + kGroups + 2;
+constexpr int kNumBars = 3 * kXStagesMax + kWStagesMax + kAStages + kGroups + 2;
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kXScale = 16.f;          // activations are multiplied by this before the split (undone in out_scale)
 
@@ -91,13 +91,13 @@ struct Tc16Params {
   int n_w;                     // weight ring depth
   int tiles_w, tiles_h, tiles_n;
   int n_chunks, ksplit;
+  int relu;                    // max(y, 0) at the store (never together with a split K range)
   long long total_pixels;      // N * OH * OW (linear mode)
   const float *out_scale;      // per output channel: 2^-sh[oc] / 16 (undoes the weight and activation scaling)
   int *error_flag;
   unsigned *gate;              // gate[0]: largest |activation| of the launch, as FP32 bits (see launch_conv_tc_gated)
   const __half *w_tiles;
-  long long *prof;             // debugging: per-role clock totals of CTA 0 (nullptr = off)
-  int dbg;                     // debugging: parts of the pipeline switched off (results are wrong then)
+  long long *prof;             // per-role clock totals of CTA 0 for TETRIS_TC16_PROF=1 (nullptr = off)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -190,14 +190,13 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
   auto bar_xempty = [&](int s) { return smem_u32(&bars[2 * kXStagesMax + s]); };
   auto bar_wfull = [&](int s) { return smem_u32(&bars[3 * kXStagesMax + s]); };
   auto bar_afull = [&](int s) { return smem_u32(&bars[3 * kXStagesMax + kWStagesMax + s]); };
-  auto bar_ready = [&](int s) { return smem_u32(&bars[3 * kXStagesMax + kWStagesMax + kAStages + s]); };
-  auto bar_gdone = [&](int c) { return smem_u32(&bars[3 * kXStagesMax + kWStagesMax + 2 * kAStages + c]); };
+  auto bar_gdone = [&](int c) { return smem_u32(&bars[3 * kXStagesMax + kWStagesMax + kAStages + c]); };
   auto bar_pempty = [&](int b) { return smem_u32(&bars[kNumBars - 2 + b]); };
 
   if (tid == 0) {
     for (int s = 0; s < kXStagesMax; ++s) { mbar_init(bar_xfull(s), 1); mbar_init(bar_xconv(s), 4); mbar_init(bar_xempty(s), 1); }
     for (int s = 0; s < kWStagesMax; ++s) mbar_init(bar_wfull(s), 1);
-    for (int s = 0; s < kAStages; ++s) { mbar_init(bar_afull(s), 1); mbar_init(bar_ready(s), 1); }
+    for (int s = 0; s < kAStages; ++s) mbar_init(bar_afull(s), 1);
     for (int c = 0; c < kGroups; ++c) mbar_init(bar_gdone(c), 1);
     for (int b = 0; b < 2; ++b) mbar_init(bar_pempty(b), 8);
     *abort_flag = 0;
@@ -211,12 +210,22 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
-  // debugging aid: clocks spent per role in total ([role * 8]) and inside each kind of wait
+  // Timeline aid, compiled in with -DTETRIS_TC16_PROF only: clocks per role of CTA 0, in total
+  // and inside its waits, printed by the launcher when the environment has TETRIS_TC16_PROF=1.
+#ifdef TETRIS_TC16_PROF
   const bool prof_on = p.prof != nullptr && blockIdx.x == 0;
   long long pw[7] = {0, 0, 0, 0, 0, 0, 0};
   const long long prof_t0 = prof_on ? clock64() : 0;
 #define TIMED(slot, expr) ([&]() { const long long t0_ = prof_on ? clock64() : 0; const bool r_ = (expr); if (prof_on) pw[slot] += clock64() - t0_; return r_; }())
 #define PROF_OUT(role) do { if (prof_on && lane == 0) { p.prof[(role) * 8] = clock64() - prof_t0; for (int i_ = 0; i_ < 7; ++i_) p.prof[(role) * 8 + 1 + i_] = pw[i_]; } } while (0)
+#define PROF_LAP(slot) do { if (prof_on) { const long long n_ = clock64(); pw[slot] += n_ - ts0; ts0 = n_; } } while (0)
+#define PROF_START() long long ts0 = prof_on ? clock64() : 0
+#else
+#define TIMED(slot, expr) (expr)
+#define PROF_OUT(role) do { } while (0)
+#define PROF_LAP(slot) do { } while (0)
+#define PROF_START() do { } while (0)
+#endif
 
   // Persistent CTA: work items blockIdx.x, blockIdx.x + gridDim.x, ...; the channel tile is the
   // fastest index, so CTAs that run side by side read the same activation patch.
@@ -276,7 +285,6 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
           const int s = G % p.n_w;
           if (G >= p.n_w && !(ok = TIMED(0, wait_pair(G - p.n_w)))) break;
           const uint32_t bytes = (uint32_t)(min(2, iters - 2 * j) * kWBytes);
-          if ((p.dbg & 2) && G >= p.n_w) { mbar_arrive(bar_wfull(s)); continue; }
           mbar_expect_tx(bar_wfull(s), bytes);
           bulk_load(smem_u32(wbase + (size_t)s * 2 * kWBytes), item + (size_t)(2 * j) * (BN * 64), bytes, bar_wfull(s));
         }
@@ -373,7 +381,7 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
         if (!(ok = TIMED(2, mbar_wait_warp(bar_wfull(sw), wphase, abort_flag)))) break;  // the pair's weights have landed
         if (!(ok = TIMED(0, mbar_wait_warp(bar_afull(sa), (G >> 2) & 1, abort_flag)))) break;  // ... and its operand blocks
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        long long ts0 = prof_on ? clock64() : 0;
+        PROF_START();
         const bool two = iters - 2 * j >= 2;
         const uint32_t ta = tmem_base + (uint32_t)(kTmemA + sa * kACols), t1 = ta + 32u;
         const uint32_t dlo = wd, d1 = wd + (uint32_t)(kWBytes >> 4);
@@ -394,9 +402,9 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
             umma_f16_ts(tmem_d, t1 + 24, d1 + 2, dw_hi, idesc, 1u);
             umma_f16_ts(tmem_d, t1 + 8, d1 + 6, dw_hi, idesc, 1u);
           }
-          if (prof_on) { const long long n_ = clock64(); pw[3] += n_ - ts0; ts0 = n_; }
+          PROF_LAP(3);
           umma_commit(bar_gdone(G & (kGroups - 1)));
-          if (prof_on) { const long long n_ = clock64(); pw[4] += n_ - ts0; ts0 = n_; }
+          PROF_LAP(4);
         }
         __syncwarp();
       }
@@ -416,7 +424,7 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
         const int sx = u % p.n_x;
         if (!(ok = TIMED(0, mbar_wait_warp(bar_xfull(sx), (u / p.n_x) & 1, abort_flag)))) break;
         unsigned char *stage = xbase + (size_t)sx * p.x_stage_bytes;
-        for (int row = ct; row < ((p.dbg & 1) ? 0 : p.box_rows); row += 128) {
+        for (int row = ct; row < p.box_rows; row += 128) {
           uint4 *rp = reinterpret_cast<uint4 *>(stage + (size_t)row * 128);
           const int sw = row & 7;
           uint4 v[8];
@@ -474,7 +482,7 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
 #pragma unroll
         for (int c0 = 0; c0 < NC; c0 += 16) {
           uint32_t v[16];
-          if (p.dbg & 4) { for (int j = 0; j < 16; ++j) v[j] = 0; } else tmem_ld16(taddr + c0, v);
+          tmem_ld16(taddr + c0, v);
           if (c0 + 16 == NC) {  // everything is in registers: the tensor core may overwrite the partial
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -503,6 +511,10 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
       float *o = p.out + pix * p.OC + ocb;
 #pragma unroll
       for (int j = 0; j < NC; ++j) acc[j] *= (ocb + j < p.OC) ? __ldg(p.out_scale + ocb + j) : 0.f;
+      if (p.relu) {
+#pragma unroll
+        for (int j = 0; j < NC; ++j) acc[j] = fmaxf(acc[j], 0.f);
+      }
       if (vec && ocb + NC <= p.OC && small_out) {
         // Coalesced path: a thread holds 32..64 channels of ONE pixel; through a 4 KiB staging
         // block per warp the rows are turned so that eight lanes write one pixel's 128
@@ -726,7 +738,7 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
     Tc16State::Setup *su = nullptr;
     for (Tc16State::Setup &c : t->setups) {
       const ConvShape &l = c.shape;
-      if (c.valid && c.in == in && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S) { su = &c; break; }
+      if (c.valid && c.in == in && l.relu == s.relu && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S) { su = &c; break; }
     }
     if (!su) {
       su = &t->setups[t->next_setup];
@@ -784,7 +796,8 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
       const double zeroing = ((double)s.N * s.OH * s.OW * s.OC * 4 / 6.0e12 + 3e-6) * 1.9e9 / 500.0;
       int best_d = 1;
       double best_cost = std::ceil((double)tiles / sms) * (iters + 12.0);
-      for (int d = 2; d <= 8 && d <= q.n_chunks && !f->deterministic; ++d) {
+      q.relu = s.relu;
+      for (int d = 2; d <= 8 && d <= q.n_chunks && !f->deterministic && !s.relu; ++d) {  // (a rectified sum cannot be added up from slices)
         if (q.n_chunks % d) continue;
         const double cost = std::ceil((double)tiles * d / sms) * (iters / d + 12.0) + zeroing;
         if (cost < 0.96 * best_cost) { best_cost = cost; best_d = d; }
@@ -800,8 +813,6 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
         --q.n_w;
         q.n_x = (int)std::min<size_t>(kXStagesMax, (kSmemBudget - fixed - q.n_w * wbytes) / q.x_stage_bytes);
       }
-      if (const char *e = getenv("TETRIS_TC16_NW")) q.n_w = std::max(2, std::min(kWStagesMax, atoi(e)));
-      if (const char *e = getenv("TETRIS_TC16_NW")) q.n_x = (int)std::min<size_t>(kXStagesMax, (kSmemBudget - fixed - q.n_w * wbytes) / q.x_stage_bytes);
       if (q.n_x < 2) { set_error("split-FP16 variant: the activation patches of this layer do not fit shared memory"); return TETRIS_ERR_UNSUPPORTED; }
       if (KS > 1) q.n_x = std::min(q.n_x, 3);          // a patch feeds KS*KS steps: three stages are ample
       q.n_x = std::max(2, std::min(q.n_x, std::max(2, chunks_per_item)));
@@ -818,6 +829,7 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
     bn = t->bn;
   }
   p.out = out;
+#ifdef TETRIS_TC16_PROF
   static long long *d_prof = nullptr;
   const bool prof = getenv("TETRIS_TC16_PROF") != nullptr;
   if (prof) {
@@ -825,7 +837,7 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
     cudaMemset(d_prof, 0, 64 * sizeof(long long));
     p.prof = d_prof;
   }
-  if (const char *e = getenv("TETRIS_TC16_DBG")) p.dbg = atoi(e);
+#endif
   static thread_local bool configured[16] = {false};
   int dev = 0;
   TETRIS_CUDA_TRY(cudaGetDevice(&dev));
@@ -842,6 +854,8 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
     conv_tc16_kernel<128><<<grid, kThreads, smem, st>>>(map_x, p);
   TETRIS_CUDA_TRY(cudaGetLastError());
   count_launch();
+  if (p.relu) note_relu_fused();
+#ifdef TETRIS_TC16_PROF
   if (prof) {
     long long h[64];
     cudaDeviceSynchronize();
@@ -854,6 +868,7 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
       fprintf(stderr, "[tc16 prof] %-42s total %9lld clk (%5.0f per K step); waits: %lld %lld %lld %lld %lld\n", names[r], h[r * 8],
               (double)h[r * 8] / (double)steps, h[r * 8 + 1], h[r * 8 + 2], h[r * 8 + 3], h[r * 8 + 4], h[r * 8 + 5]);
   }
+#endif
   // The guard: the split-TF32 variant, queued behind; it returns at once unless the largest
   // activation of this launch lies outside FP16's useful window, in which case it recomputes the layer.
   return launch_conv_tc_gated(f, in, out, s, st, t->d_gate);

@@ -47,6 +47,7 @@ void set_error(const char *fmt, ...);
 
 struct ConvShape {
   int N, H, W, IC, OC, KS, S, P, OH, OW;
+  int relu = 0;  // fused epilogue: max(y, 0) at the store (tetris_conv2d_launch_fused)
 };
 
 // compress.cu: dense filter on the device -> program stream.  `d_scratch` holds
@@ -99,6 +100,11 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
 int conv_tc16_check_error(const tetris_filter *f);
 int launch_depthwise(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                      cudaStream_t st);
+// chain.cu / api.cu: y = max(y, 0) in place; an automatic launch of one conv (with its fused
+// options in s); whether the launch at hand rectified at its own store
+int launch_relu_inplace(float *y, size_t n, cudaStream_t st);
+int conv_dispatch_auto(const tetris_filter *f, const float *in, float *out, const ConvShape &s, cudaStream_t st);
+void note_relu_fused();
 int launch_nchw_to_nhwc(const float *src, float *dst, int N, int C, int H, int W, cudaStream_t st);
 int launch_nhwc_to_nchw(const float *src, float *dst, int N, int C, int H, int W, cudaStream_t st);
 
