@@ -48,7 +48,8 @@
 // freed and the kernel returns; the host reports TETRIS_ERR_CUDA.
 //
 // 1x1 filters take the same pipeline with M = 128 consecutive pixels of the flattened image
-// (no halo, 100 % full tiles).  Covers stride 1, IC % 4 == 0 (TMA strides), KS <= 7.
+// (no halo, 100 % full tiles).  Mid-size images (28 x 28, 52 x 52 ...), which 8 x 16 tiles cut
+// badly, are walked in their padded-width layout instead (`flat`, see launch_conv_tc16).  Covers stride 1, IC % 4 == 0 (TMA strides), KS <= 7.
 // No cluster launch: every load is issued by one CTA for itself.
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -83,7 +84,9 @@ struct Tc16Params {
   float *out;
   int N, OH, OW, OC, P, KS;
   int linear;                  // 1x1 filters: a tile is 128 consecutive pixels of the flattened N*OH*OW image
-  int PW;                      // patch width in pixels (kTW + KS - 1); 8 in linear mode
+  int flat;                    // a tile is 128 consecutive positions of one image laid out with its padded width
+                               // PW = W + 2P (positions past OW in a row are computed and dropped)
+  int PW;                      // patch width in pixels (kTW + KS - 1; flat mode: W + 2P); 8 in linear mode
   int PHI;                     // patch rows one image occupies in a stage
   int TH, NB;                  // output rows and images of a tile
   int box_rows;                // 128-byte rows a patch load delivers
@@ -264,6 +267,9 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
           mbar_expect_tx(bar_xfull(s), box_bytes);
           if (p.linear)
             tma_load_4d(smem_u32(xbase + (size_t)s * p.x_stage_bytes), &map_x, bar_xfull(s), chunk * KC, (w0 / kTW) * BM, 0, 0);
+          else if (p.flat)  // whole padded rows, from the row above the tile's first output row
+            tma_load_4d(smem_u32(xbase + (size_t)s * p.x_stage_bytes), &map_x, bar_xfull(s), chunk * KC, -p.P,
+                        ((w0 / kTW) * BM) / p.PW - p.P, n0);
           else
             tma_load_4d(smem_u32(xbase + (size_t)s * p.x_stage_bytes), &map_x, bar_xfull(s), chunk * KC, w0 - p.P, h0 - p.P, n0);
           if (++s == p.n_x) { s = 0; phase ^= 1u; }
@@ -297,7 +303,7 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
     //      the converted patch -> the step's operand block in tensor memory; one wait and one
     //      commit per pair.  Everything that depends on the K step is counted along: the issuing
     //      thread's own instructions, not the tensor unit, set the pace otherwise. ----
-    const uint32_t sbo = (uint32_t)(p.linear ? 1024 : p.PW * 128);
+    const uint32_t sbo = (uint32_t)((p.linear || p.flat) ? 1024 : p.PW * 128);
     const uint32_t da_hi = (uint32_t)(smem_desc(0, sbo) >> 32);
     const uint32_t x0 = (uint32_t)smem_desc(smem_u32(xbase), sbo);       // descriptor (low word) of stage 0, tap (0, 0)
     const uint32_t stage_step = (uint32_t)(p.x_stage_bytes >> 4);        // ... one stage further
@@ -309,6 +315,13 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
     bool ok = true;
     for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
       int r = 0, q = 0;  // tap of the next K step
+      // flat mode: the tile's first position lies (P0 mod PW) rows into its first padded row
+      uint32_t td0 = 0;
+      if (p.flat) {
+        const int P0 = ((t / (p.ksplit * oc_tiles)) % p.tiles_w) * BM;
+        td0 = (uint32_t)((P0 - (P0 / p.PW) * p.PW) * 8);
+      }
+      td = td0;
       for (int j = 0; j < npairs; ++j, ++G) {
         const int sa = G & (kAStages - 1);
         const bool two = iters - 2 * j >= 2;
@@ -329,14 +342,14 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
         const uint32_t a0 = xd + td;
         const int sx0 = sx;
         const bool last0 = r == p.KS - 1 && q == p.KS - 1;
-        if (last0) { r = 0; q = 0; td = 0; if (++sx == p.n_x) { sx = 0; xd = x0; xphase ^= 1u; } else xd += stage_step; }
+        if (last0) { r = 0; q = 0; td = td0; if (++sx == p.n_x) { sx = 0; xd = x0; xphase ^= 1u; } else xd += stage_step; }
         else if (++q == p.KS) { q = 0; ++r; td += row_step; }
         else td += 8;
         const uint32_t a1 = xd + td;
         const int sx1 = sx;
         const bool last1 = two && r == p.KS - 1 && q == p.KS - 1;
         if (two) {
-          if (last1) { r = 0; q = 0; td = 0; if (++sx == p.n_x) { sx = 0; xd = x0; xphase ^= 1u; } else xd += stage_step; }
+          if (last1) { r = 0; q = 0; td = td0; if (++sx == p.n_x) { sx = 0; xd = x0; xphase ^= 1u; } else xd += stage_step; }
           else if (++q == p.KS) { q = 0; ++r; td += row_step; }
           else td += 8;
         }
@@ -465,7 +478,7 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
     const int quarter = warp & 3, half = (warp - 8) >> 2;
     const int row = quarter * 32 + lane;   // tile row = pixel = TMEM lane
     const int gx = row & 7, grp = row >> 3;
-    const int pn = p.linear ? 0 : grp / p.PHI, ph = p.linear ? 0 : grp - pn * p.PHI;
+    const int pn = (p.linear || p.flat) ? 0 : grp / p.PHI, ph = (p.linear || p.flat) ? 0 : grp - pn * p.PHI;
     const bool vec = (p.OC & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
     const bool small_out = (unsigned long long)p.N * p.OH * p.OW * p.OC < (1ull << 34);  // 32-bit offsets in 16-byte units
     int gbase = 0, sp = 0;  // first pair of the item; partial sum, counted across items
@@ -501,6 +514,10 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
         const long long px = (long long)(w0 / kTW) * BM + row;
         row_ok = px < p.total_pixels;
         pix = (size_t)px;
+      } else if (p.flat) {
+        const int pos = (w0 / kTW) * BM + row, oh = pos / p.PW, ow = pos - oh * p.PW;
+        row_ok = ow < p.OW && oh < p.OH && n0 < p.N;
+        pix = ((size_t)n0 * p.OH + oh) * p.OW + ow;
       } else {
         const int ow = w0 + gx, oh = h0 + ph, n = n0 + pn;
         row_ok = pn < p.NB && ph < p.TH && ow < p.OW && oh < p.OH && n < p.N;
@@ -770,6 +787,26 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
         q.tiles_w = (s.OW + kTW - 1) / kTW;
         q.tiles_h = (s.OH + q.TH - 1) / q.TH;
         q.tiles_n = (s.N + q.NB - 1) / q.NB;
+        // The other geometry: the image laid out with its padded width Wp = W + 2P, a tile = 128
+        // consecutive positions of that layout (8-pixel groups simply follow one another, so a
+        // window is again one descriptor).  Nothing is lost to tile shapes -- only the Wp - OW
+        // positions per row that are no outputs -- at the price of a patch of whole padded rows.
+        // Taken when it needs fewer tiles and the patches still fit beside three weight stages.
+        const int Wp = s.W + 2 * s.P;
+        const int span = (Wp - 1 + BM - 1) / Wp + 1;            // output rows a tile can touch
+        const int nrows = span + halo;
+        const long long tiles_flat = (long long)(((long long)s.OH * Wp + BM - 1) / BM) * s.N;
+        const long long tiles_2d = (long long)q.tiles_w * q.tiles_h * q.tiles_n;
+        const size_t flat_stage = ((size_t)(Wp * nrows + 8) * 128 + 1023) / 1024 * 1024;
+        const size_t room = kSmemBudget - (1024 + kStoreBytes + kNumBars * 8 + 16) - 3 * (size_t)t->bn * 256;
+        // (with room for two patches only -- a pair of K steps may need both -- it has to save 10 % of the tiles)
+        if (Wp <= 256 && nrows <= 256 &&
+            ((3 * flat_stage <= room && tiles_flat * 100 < tiles_2d * 97) || (2 * flat_stage <= room && tiles_flat * 100 < tiles_2d * 90))) {
+          q.flat = 1;
+          q.PW = Wp; q.PHI = nrows; q.TH = s.OH; q.NB = 1;
+          q.box_rows = Wp * nrows;
+          q.tiles_w = (int)(((long long)s.OH * Wp + BM - 1) / BM); q.tiles_h = 1; q.tiles_n = s.N;
+        }
         dims[0] = (cuuint64_t)s.IC; dims[1] = (cuuint64_t)s.W; dims[2] = (cuuint64_t)s.H; dims[3] = (cuuint64_t)s.N;
         strides[0] = (cuuint64_t)s.IC * 4; strides[1] = strides[0] * s.W; strides[2] = strides[1] * s.H;
         box[0] = KC; box[1] = (cuuint32_t)q.PW; box[2] = (cuuint32_t)q.PHI; box[3] = (cuuint32_t)q.NB;
@@ -779,7 +816,7 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return TETRIS_ERR_CUDA; }
       // a stage holds the patch and whatever the windows of the 16 groups reach beyond it
-      const int reach_rows = q.linear ? BM : (kTH + halo) * q.PW + halo + 8;
+      const int reach_rows = q.linear ? BM : q.flat ? q.box_rows + 8 : (kTH + halo) * q.PW + halo + 8;
       q.x_stage_bytes = (std::max(reach_rows, q.box_rows) * 128 + 1023) / 1024 * 1024;
       q.n_chunks = t->n_chunks;
       q.w_tiles = t->d_tiles;

@@ -13,21 +13,24 @@
 namespace tetris {
 namespace {
 
-// 3x3, stride S, four channels per thread, TW output columns per thread.
-template <int S, int TW>
+// 3x3, stride S, four channels per thread, TW output columns x RH output rows per thread.  The
+// input rows are walked once: row `i` of the thread's window contributes to every output row
+// whose three taps cover it, so an input value is loaded once per thread, not once per output row
+// (with one output row per thread the L2 -> SM traffic measured 3.2x the input).
+template <int S, int TW, int RH>
 __global__ void __launch_bounds__(256)
 depthwise3x3_kernel(const float4 *__restrict__ in, float4 *__restrict__ out,
-                    const float *__restrict__ filt, ConvShape s, int cq, int wtiles) {
+                    const float *__restrict__ filt, ConvShape s, int cq, int wtiles, int htiles) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long total = (long long)s.N * s.OH * wtiles * cq;
+  const long long total = (long long)s.N * htiles * wtiles * cq;
   if (idx >= total) return;
   const int q = (int)(idx % cq);
   long long rest = idx / cq;
   const int wt = (int)(rest % wtiles);
   rest /= wtiles;
-  const int oh = (int)(rest % s.OH);
-  const int n = (int)(rest / s.OH);
-  const int ow0 = wt * TW;
+  const int ht = (int)(rest % htiles);
+  const int n = (int)(rest / htiles);
+  const int ow0 = wt * TW, oh0 = ht * RH;
 
   float4 w[9];
 #pragma unroll
@@ -37,16 +40,22 @@ depthwise3x3_kernel(const float4 *__restrict__ in, float4 *__restrict__ out,
     w[t].z = __ldg(&filt[(size_t)(4 * q + 2) * 9 + t]);
     w[t].w = __ldg(&filt[(size_t)(4 * q + 3) * 9 + t]);
   }
-  float4 acc[TW];
+  float4 acc[RH][TW];
 #pragma unroll
-  for (int j = 0; j < TW; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int a = 0; a < RH; ++a)
+#pragma unroll
+    for (int j = 0; j < TW; ++j) acc[a][j] = make_float4(0.f, 0.f, 0.f, 0.f);
 
   constexpr int NCOL = (TW - 1) * S + 3;  // input columns this thread touches per row
-  const int iw0 = ow0 * S - s.P;
+  constexpr int NROW = (RH - 1) * S + 3;  // input rows of its window
+  const int iw0 = ow0 * S - s.P, ih0 = oh0 * S - s.P;
   const float4 *img = in + (size_t)n * s.H * s.W * cq + q;
+  // Taps are added in (r, s) order per output, the order of the CPU loop nest
+  // (Tetris/tensor_utils.cc:152-153): window row i serves output row a with filter row r = i - a*S,
+  // and i ascends.
 #pragma unroll
-  for (int r = 0; r < 3; ++r) {
-    const int ih = oh * S + r - s.P;
+  for (int i = 0; i < NROW; ++i) {
+    const int ih = ih0 + i;
     if (ih < 0 || ih >= s.H) continue;
     float4 x[NCOL];
 #pragma unroll
@@ -56,20 +65,29 @@ depthwise3x3_kernel(const float4 *__restrict__ in, float4 *__restrict__ out,
                                    : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
-    for (int j = 0; j < TW; ++j)
+    for (int a = 0; a < RH; ++a) {
+      const int r = i - a * S;
+      if (r < 0 || r > 2) continue;
 #pragma unroll
-      for (int t = 0; t < 3; ++t) {
-        const float4 xv = x[j * S + t], wv = w[r * 3 + t];
-        acc[j].x = fmaf(wv.x, xv.x, acc[j].x);
-        acc[j].y = fmaf(wv.y, xv.y, acc[j].y);
-        acc[j].z = fmaf(wv.z, xv.z, acc[j].z);
-        acc[j].w = fmaf(wv.w, xv.w, acc[j].w);
-      }
+      for (int j = 0; j < TW; ++j)
+#pragma unroll
+        for (int t = 0; t < 3; ++t) {
+          const float4 xv = x[j * S + t], wv = w[r * 3 + t];
+          acc[a][j].x = fmaf(wv.x, xv.x, acc[a][j].x);
+          acc[a][j].y = fmaf(wv.y, xv.y, acc[a][j].y);
+          acc[a][j].z = fmaf(wv.z, xv.z, acc[a][j].z);
+          acc[a][j].w = fmaf(wv.w, xv.w, acc[a][j].w);
+        }
+    }
   }
-  float4 *o = out + (((size_t)n * s.OH + oh) * s.OW + ow0) * cq + q;
 #pragma unroll
-  for (int j = 0; j < TW; ++j)
-    if (ow0 + j < s.OW) o[(size_t)j * cq] = acc[j];
+  for (int a = 0; a < RH; ++a) {
+    if (oh0 + a >= s.OH) continue;
+    float4 *o = out + (((size_t)n * s.OH + oh0 + a) * s.OW + ow0) * cq + q;
+#pragma unroll
+    for (int j = 0; j < TW; ++j)
+      if (ow0 + j < s.OW) o[(size_t)j * cq] = acc[a][j];
+  }
 }
 
 // Any kernel size / stride / channel count: one output element per thread.
@@ -111,14 +129,26 @@ int launch_depthwise(const tetris_filter *f, const float *in, float *out, const 
   if (vec) {
     constexpr int TW = 4;
     const int cq = s.OC / 4, wtiles = (s.OW + TW - 1) / TW;
-    const long long threads = (long long)s.N * s.OH * wtiles * cq;
-    const unsigned blocks = (unsigned)((threads + 255) / 256);
     const float4 *in4 = reinterpret_cast<const float4 *>(in);
     float4 *out4 = reinterpret_cast<float4 *>(out);
-    if (s.S == 1)
-      depthwise3x3_kernel<1, TW><<<blocks, 256, 0, st>>>(in4, out4, f->d_dense, s, cq, wtiles);
+    // Two output rows per thread where that still leaves a few thousand threads per SM in flight;
+    // one row on the small late layers, where parallelism is what is short.
+    int dev = 0, sms = 0;
+    TETRIS_CUDA_TRY(cudaGetDevice(&dev));
+    TETRIS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long threads1 = (long long)s.N * s.OH * wtiles * cq;
+    const int RH = threads1 >= (long long)sms * 2048 * 2 ? 2 : 1;
+    const int htiles = (s.OH + RH - 1) / RH;
+    const long long threads = (long long)s.N * htiles * wtiles * cq;
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+    if (s.S == 1 && RH == 2)
+      depthwise3x3_kernel<1, TW, 2><<<blocks, 256, 0, st>>>(in4, out4, f->d_dense, s, cq, wtiles, htiles);
+    else if (s.S == 1)
+      depthwise3x3_kernel<1, TW, 1><<<blocks, 256, 0, st>>>(in4, out4, f->d_dense, s, cq, wtiles, htiles);
+    else if (RH == 2)
+      depthwise3x3_kernel<2, TW, 2><<<blocks, 256, 0, st>>>(in4, out4, f->d_dense, s, cq, wtiles, htiles);
     else
-      depthwise3x3_kernel<2, TW><<<blocks, 256, 0, st>>>(in4, out4, f->d_dense, s, cq, wtiles);
+      depthwise3x3_kernel<2, TW, 1><<<blocks, 256, 0, st>>>(in4, out4, f->d_dense, s, cq, wtiles, htiles);
   } else {
     depthwise_any_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, st>>>(in, out, f->d_dense, s);
   }
