@@ -43,6 +43,7 @@ def build(force=False, verbose=False):
     if not force and not needs_build():
         return LIB
     cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else [])
+    cmd += os.environ.get("TETRIS_NVCC_FLAGS", "").split()  # e.g. -DTETRIS_TC16_PROF: the kernel timeline aid
     cmd += ["-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose:

@@ -94,6 +94,12 @@ struct Tc16Params {
   int n_w;                     // weight ring depth
   int tiles_w, tiles_h, tiles_n;
   int n_chunks, ksplit;
+  // Tail split: the tiles that would form a last, nearly empty wave of CTAs (tiles tail_tile0 ...)
+  // are cut into tail_d K slices each (work items tail_start ...); the slices leave their sums in
+  // `scratch`, and whichever finishes last (tail_count) adds them up in slice order and stores.
+  int tail_start, tail_tile0, tail_d;
+  float *scratch;
+  int *tail_count;
   int relu;                    // max(y, 0) at the store (never together with a split K range)
   long long total_pixels;      // N * OH * OW (linear mode)
   const float *out_scale;      // per output channel: 2^-sh[oc] / 16 (undoes the weight and activation scaling)
@@ -233,14 +239,27 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
   // Persistent CTA: work items blockIdx.x, blockIdx.x + gridDim.x, ...; the channel tile is the
   // fastest index, so CTAs that run side by side read the same activation patch.
   const int taps = p.KS * p.KS;
-  const int item_chunks = p.n_chunks / p.ksplit;          // chunks of a work item (ksplit divides n_chunks)
-  const int iters = taps * item_chunks;                   // K steps of a work item
-  const int npairs = (iters + 1) / 2;                     // the pipeline's unit is a PAIR of K steps (the last may be single)
-  const int tile_supers = (npairs + kSuper - 1) / kSuper; // partial accumulators of a work item
   const int oc_tiles = (p.OC + BN - 1) / BN;
-  const int total_items = p.tiles_w * p.tiles_h * p.tiles_n * oc_tiles * p.ksplit;
-  auto decode = [&](int t, int &w0, int &h0, int &n0, int &oc0, int &chunk0) {
-    chunk0 = (t % p.ksplit) * item_chunks; t /= p.ksplit;
+  const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_n * oc_tiles;
+  const int total_items = p.tail_start + (total_tiles - p.tail_tile0) * p.tail_d;
+  // A work item is a tile, or one of ksplit equal slices of a tile's K range (all tiles), or --
+  // for the tiles of the last wave -- one of tail_d slices.  The pipeline's unit is a PAIR of K
+  // steps (the last of an item may be single).
+  struct Item { int tile, chunk0, chunks, iters, npairs, supers; bool tail; int slice; };
+  auto item_of = [&](int t) {
+    Item it;
+    it.tail = t >= p.tail_start;
+    const int d = it.tail ? p.tail_d : p.ksplit, u = it.tail ? t - p.tail_start : t;
+    it.slice = u % d;
+    it.tile = (it.tail ? p.tail_tile0 : 0) + u / d;
+    it.chunks = p.n_chunks / d;
+    it.chunk0 = it.slice * it.chunks;
+    it.iters = taps * it.chunks;
+    it.npairs = (it.iters + 1) / 2;
+    it.supers = (it.npairs + kSuper - 1) / kSuper;
+    return it;
+  };
+  auto decode = [&](int t, int &w0, int &h0, int &n0, int &oc0) {
     oc0 = (t % oc_tiles) * BN; t /= oc_tiles;
     w0 = (t % p.tiles_w) * kTW; t /= p.tiles_w;       // (linear mode: tiles_w = number of 128-pixel tiles)
     h0 = (t % p.tiles_h) * p.TH;
@@ -260,9 +279,10 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
       uint32_t phase = 1;  // (a fresh barrier lets the first lap through)
       bool ok = true;
       for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
-        int w0, h0, n0, oc0, chunk0;
-        decode(t, w0, h0, n0, oc0, chunk0);
-        for (int chunk = chunk0; chunk < chunk0 + item_chunks; ++chunk) {
+        const Item it = item_of(t);
+        int w0, h0, n0, oc0;
+        decode(it.tile, w0, h0, n0, oc0);
+        for (int chunk = it.chunk0; chunk < it.chunk0 + it.chunks; ++chunk) {
           if (!(ok = TIMED(0, mbar_wait(bar_xempty(s), phase, abort_flag)))) break;
           mbar_expect_tx(bar_xfull(s), box_bytes);
           if (p.linear)
@@ -284,9 +304,11 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
       int G = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
-        int w0, h0, n0, oc0, chunk0;
-        decode(t, w0, h0, n0, oc0, chunk0);
-        const __half *item = p.w_tiles + ((size_t)(oc0 / BN) * p.n_chunks + chunk0) * taps * (size_t)(BN * 64);
+        const Item it = item_of(t);
+        const int iters = it.iters, npairs = it.npairs;
+        int w0, h0, n0, oc0;
+        decode(it.tile, w0, h0, n0, oc0);
+        const __half *item = p.w_tiles + ((size_t)(oc0 / BN) * p.n_chunks + it.chunk0) * taps * (size_t)(BN * 64);
         for (int j = 0; j < npairs; ++j, ++G) {
           const int s = G % p.n_w;
           if (G >= p.n_w && !(ok = TIMED(0, wait_pair(G - p.n_w)))) break;
@@ -316,9 +338,11 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
     for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
       int r = 0, q = 0;  // tap of the next K step
       // flat mode: the tile's first position lies (P0 mod PW) rows into its first padded row
+      const Item it = item_of(t);
+      const int iters = it.iters, npairs = it.npairs;
       uint32_t td0 = 0;
       if (p.flat) {
-        const int P0 = ((t / (p.ksplit * oc_tiles)) % p.tiles_w) * BM;
+        const int P0 = ((it.tile / oc_tiles) % p.tiles_w) * BM;
         td0 = (uint32_t)((P0 - (P0 / p.PW) * p.PW) * 8);
       }
       td = td0;
@@ -381,11 +405,15 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
     int G = 0, sw = 0, sbase = 0, sp = 0;
     uint32_t wd = w0, wphase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x, sbase += tile_supers) {
+    for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
+      const Item it = item_of(t);
+      const int iters = it.iters, npairs = it.npairs;
+      const int sbase0 = sbase;
+      sbase += it.supers;
       for (int j = 0, jj = 0, si = 0; j < npairs; ++j, ++G) {
         const int sa = G & (kAStages - 1);
         const uint32_t acc0 = jj == 0 ? 0u : 1u;  // the first MMA of a partial overwrites it
-        const uint32_t tmem_d = tmem_base + (uint32_t)(((sbase + si) & 1) * BN);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(((sbase0 + si) & 1) * BN);
         if (jj == 0) {  // first pair of a partial sum: its accumulator has been drained (two partials ago)
           if (!(ok = TIMED(1, mbar_wait_warp(bar_pempty(sp & 1), ((sp >> 1) & 1) ^ 1, abort_flag)))) break;
           ++sp;
@@ -433,6 +461,7 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
     bool ok = true;
     uint32_t seen_max = 0;
     for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
+      const int item_chunks = item_of(t).chunks;
       for (int chunk = 0; chunk < item_chunks; ++chunk, ++u) {
         const int sx = u % p.n_x;
         if (!(ok = TIMED(0, mbar_wait_warp(bar_xfull(sx), (u / p.n_x) & 1, abort_flag)))) break;
@@ -477,19 +506,38 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
     constexpr int NC = BN / 2;             // channels per thread
     const int quarter = warp & 3, half = (warp - 8) >> 2;
     const int row = quarter * 32 + lane;   // tile row = pixel = TMEM lane
-    const int gx = row & 7, grp = row >> 3;
-    const int pn = (p.linear || p.flat) ? 0 : grp / p.PHI, ph = (p.linear || p.flat) ? 0 : grp - pn * p.PHI;
     const bool vec = (p.OC & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
     const bool small_out = (unsigned long long)p.N * p.OH * p.OW * p.OC < (1ull << 34);  // 32-bit offsets in 16-byte units
+    // output pixel of tile row r of the tile at (w0, h0, n0), in the launch's tile geometry
+    auto row_pixel = [&](int r, int w0, int h0, int n0, bool &okr, size_t &pix) {
+      if (p.linear) {
+        const long long px = (long long)(w0 / kTW) * BM + r;
+        okr = px < p.total_pixels;
+        pix = (size_t)px;
+      } else if (p.flat) {
+        const int pos = (w0 / kTW) * BM + r, oh = pos / p.PW, ow = pos - oh * p.PW;
+        okr = ow < p.OW && oh < p.OH && n0 < p.N;
+        pix = ((size_t)n0 * p.OH + oh) * p.OW + ow;
+      } else {
+        const int g = r >> 3, in = g / p.PHI, ih = g - in * p.PHI;
+        const int ow = w0 + (r & 7), oh = h0 + ih, n = n0 + in;
+        okr = in < p.NB && ih < p.TH && ow < p.OW && oh < p.OH && n < p.N;
+        pix = ((size_t)n * p.OH + oh) * p.OW + ow;
+      }
+    };
     int gbase = 0, sp = 0;  // first pair of the item; partial sum, counted across items
     bool ok = true;
-    for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x, gbase += npairs) {
+    for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
+      int npairs, tile_supers;
+      { const Item head = item_of(t); npairs = head.npairs; tile_supers = head.supers; }
+      const int gbase0 = gbase;
+      gbase += npairs;
       float acc[NC];
 #pragma unroll
       for (int j = 0; j < NC; ++j) acc[j] = 0.f;
       for (int si = 0; si < tile_supers; ++si, ++sp) {
         const int b = sp & 1;
-        if (!(ok = TIMED(0, wait_pair_warp(gbase + min((si + 1) * kSuper, npairs) - 1)))) break;  // the partial's last pair
+        if (!(ok = TIMED(0, wait_pair_warp(gbase0 + min((si + 1) * kSuper, npairs) - 1)))) break;  // the partial's last pair
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + half * NC);
 #pragma unroll
@@ -506,23 +554,77 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
         }
       }
       if (!ok) break;
-      int w0, h0, n0, oc0, chunk0;
-      decode(t, w0, h0, n0, oc0, chunk0);
+      // (the item is worked out again here rather than kept in registers across the sums above:
+      // with 64 running sums per thread this role is the one that sets the kernel's register count)
+      int t_again = t;
+      asm volatile("" : "+r"(t_again));
+      const Item it = item_of(t_again);
+      int w0, h0, n0, oc0;
+      decode(it.tile, w0, h0, n0, oc0);
+      PROF_START();
+      if (it.tail) {
+        // A slice of a last-wave tile: leave the partial sums in the scratch block of (tile,
+        // slice); the CTA that finishes a tile last adds the slices up in slice order (so the
+        // result does not depend on who that is) and carries on to the store.
+        float4 *mine = reinterpret_cast<float4 *>(p.scratch + ((size_t)((it.tile - p.tail_tile0) * p.tail_d + it.slice) * BM + row) * BN + half * NC);
+#pragma unroll
+        for (int j = 0; j < NC; j += 4) mine[j >> 2] = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        __threadfence();
+        PROF_LAP(2);
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight summing warps
+        int *verdict = reinterpret_cast<int *>(store_base);  // (the staging block is free between items)
+        if (warp == 8 && lane == 0) {
+          const int seen = atomicAdd(p.tail_count + (it.tile - p.tail_tile0), 1);
+          *verdict = seen == p.tail_d - 1 ? 1 : 0;
+          if (seen == p.tail_d - 1) p.tail_count[it.tile - p.tail_tile0] = 0;  // ready for the next launch
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const bool reducer = *verdict != 0;
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // (the staging block is written again below)
+        PROF_LAP(3);
+        if (!reducer) continue;
+        __threadfence();
+        // The slices are added position by position (a warp walks one row of the tile: coalesced
+        // reads of the eight scratch blocks, coalesced stores) rather than into the per-thread
+        // running sums: with those 64 registers held, the loads of the slices would go out one
+        // at a time (measured: 36 us for one tile).
+        constexpr int V = BN / 4;  // 16-byte pieces per tile row
+        const float4 *blocks = reinterpret_cast<const float4 *>(p.scratch + (size_t)(it.tile - p.tail_tile0) * p.tail_d * BM * BN);
+        const bool vec_out = (p.OC & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+        for (int idx = (warp - 8) * 32 + lane; idx < BM * V; idx += 256) {
+          float4 v[8];
+#pragma unroll
+          for (int sl = 0; sl < 8; ++sl)
+            v[sl] = sl < p.tail_d ? __ldcg(blocks + (size_t)sl * BM * V + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+          float4 sum = v[0];
+#pragma unroll
+          for (int sl = 1; sl < 8; ++sl) { sum.x += v[sl].x; sum.y += v[sl].y; sum.z += v[sl].z; sum.w += v[sl].w; }
+          const int r2 = idx / V, oc = oc0 + 4 * (idx - r2 * V);
+          bool ok2;
+          size_t pix2;
+          row_pixel(r2, w0, h0, n0, ok2, pix2);
+          if (!ok2 || oc >= p.OC || *abort_flag) continue;
+          float res[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            res[e] *= (oc + e < p.OC) ? __ldg(p.out_scale + oc + e) : 0.f;
+            if (p.relu) res[e] = fmaxf(res[e], 0.f);
+          }
+          float *dst = p.out + pix2 * p.OC + oc;
+          if (vec_out) *reinterpret_cast<float4 *>(dst) = make_float4(res[0], res[1], res[2], res[3]);
+          else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (oc + e < p.OC) dst[e] = res[e];
+          }
+        }
+        PROF_LAP(4);
+        continue;
+      }
+      const bool add_up = !it.tail && p.ksplit > 1;  // a slice of a uniformly split K range: add into the zeroed output
       bool row_ok;
       size_t pix;
-      if (p.linear) {
-        const long long px = (long long)(w0 / kTW) * BM + row;
-        row_ok = px < p.total_pixels;
-        pix = (size_t)px;
-      } else if (p.flat) {
-        const int pos = (w0 / kTW) * BM + row, oh = pos / p.PW, ow = pos - oh * p.PW;
-        row_ok = ow < p.OW && oh < p.OH && n0 < p.N;
-        pix = ((size_t)n0 * p.OH + oh) * p.OW + ow;
-      } else {
-        const int ow = w0 + gx, oh = h0 + ph, n = n0 + pn;
-        row_ok = pn < p.NB && ph < p.TH && ow < p.OW && oh < p.OH && n < p.N;
-        pix = ((size_t)n * p.OH + oh) * p.OW + ow;
-      }
+      row_pixel(row, w0, h0, n0, row_ok, pix);
       row_ok = row_ok && !*abort_flag;
       const int ocb = oc0 + half * NC;
       float *o = p.out + pix * p.OC + ocb;
@@ -557,7 +659,7 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
             const uint32_t off = __shfl_sync(0xffffffffu, off16, 4 * i + (lane >> 3));
             float *dst = p.out + ((size_t)off << 2) + h * 32 + 4 * qq;
             if (off != 0xFFFFFFFFu) {
-              if (p.ksplit > 1)  // a slice of the K range: add into the zeroed output
+              if (add_up)
                 asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v[i].x), "f"(v[i].y), "f"(v[i].z), "f"(v[i].w) : "memory");
               else
                 *reinterpret_cast<float4 *>(dst) = v[i];
@@ -568,7 +670,7 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
         continue;
       }
       if (!row_ok) continue;
-      if (p.ksplit > 1) {
+      if (add_up) {
 #pragma unroll
         for (int j = 0; j < NC; ++j)
           if (ocb + j < p.OC) atomicAdd(o + j, acc[j]);
@@ -662,6 +764,9 @@ struct Tc16State {
   unsigned *d_gate = nullptr;
   int n_chunks = 0, bn = 128;
   float *d_out_scale = nullptr;  // per output channel
+  float *d_scratch = nullptr;    // tail split: one 128 x BN block of partial sums per CTA
+  int *d_tail_count = nullptr;   // tail split: finished slices per last-wave tile (all zero between launches)
+  int sms = 0;
   struct Setup {
     bool valid = false;
     const float *in = nullptr;
@@ -685,6 +790,7 @@ void conv_tc16_state_delete(void *state) {
   Tc16State *s = static_cast<Tc16State *>(state);
   if (!s) return;
   cudaFree(s->d_tiles); cudaFree(s->d_error); cudaFree(s->d_gate); cudaFree(s->d_out_scale);
+  cudaFree(s->d_scratch); cudaFree(s->d_tail_count);
   delete s;
 }
 
@@ -700,14 +806,19 @@ int conv_tc16_prepare(tetris_filter *f, const float *d_dense) {
   s->bn = f->out_channel <= 64 ? 64 : 128;
   const int oc_tiles = (f->out_channel + s->bn - 1) / s->bn;
   const size_t elems = (size_t)taps * s->n_chunks * oc_tiles * s->bn * 64;
-  if (cudaMalloc(&s->d_tiles, elems * sizeof(__half)) != cudaSuccess || cudaMalloc(&s->d_error, sizeof(int)) != cudaSuccess ||
-      cudaMalloc(&s->d_gate, 2 * sizeof(unsigned)) != cudaSuccess) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&s->sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) s->sms = 0;
+  if (s->sms < 1 || cudaMalloc(&s->d_tiles, elems * sizeof(__half)) != cudaSuccess || cudaMalloc(&s->d_error, sizeof(int)) != cudaSuccess ||
+      cudaMalloc(&s->d_gate, 2 * sizeof(unsigned)) != cudaSuccess ||
+      cudaMalloc(&s->d_scratch, (size_t)s->sms * BM * s->bn * sizeof(float)) != cudaSuccess ||
+      cudaMalloc(&s->d_tail_count, (size_t)s->sms * sizeof(int)) != cudaSuccess) {
     cudaGetLastError();
     conv_tc16_state_delete(s);
     return TETRIS_OK;
   }
   cudaMemset(s->d_error, 0, sizeof(int));
   cudaMemset(s->d_gate, 0, 2 * sizeof(unsigned));
+  cudaMemset(s->d_tail_count, 0, (size_t)s->sms * sizeof(int));
   // per-channel scales: every output channel's largest |w| lands in [2^12, 2^13)
   float *d_w_scale = nullptr;
   if (cudaMalloc(&d_w_scale, f->out_channel * sizeof(float)) != cudaSuccess ||
@@ -840,6 +951,19 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
         if (cost < 0.96 * best_cost) { best_cost = cost; best_d = d; }
       }
       q.ksplit = best_d;
+      // Tail split: with T tiles on S CTAs the last wave holds T mod S tiles; when that is a small
+      // remainder, each of those tiles is cut into d K slices (d a divisor of the chunk count, at
+      // most one slice per CTA) that run side by side and are added up through the scratch blocks
+      // -- in slice order, so the result stays bit-reproducible, and with no zeroing of the output.
+      q.tail_tile0 = (int)tiles; q.tail_start = (int)tiles * best_d; q.tail_d = 1;
+      q.scratch = t->d_scratch; q.tail_count = t->d_tail_count;
+      if (best_d == 1 && tiles > sms && sms <= t->sms) {
+        const int full = (int)(tiles / sms) * sms, rest = (int)tiles - full;
+        int d = 0;
+        for (int c = 2; c <= 8 && c <= q.n_chunks; ++c)
+          if (q.n_chunks % c == 0 && rest * c <= sms) d = c;
+        if (rest > 0 && d >= 2) { q.tail_tile0 = full; q.tail_start = full; q.tail_d = d; }
+      }
       // shared memory: activation ring, weight ring, store staging, barriers
       const size_t wbytes = (size_t)t->bn * 128 * 2;  // a weight stage holds a pair of K steps
       const size_t fixed = 1024 + kStoreBytes + kNumBars * 8 + 16;
@@ -854,7 +978,7 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
       if (KS > 1) q.n_x = std::min(q.n_x, 3);          // a patch feeds KS*KS steps: three stages are ample
       q.n_x = std::max(2, std::min(q.n_x, std::max(2, chunks_per_item)));
       su->smem = fixed + (size_t)q.n_x * q.x_stage_bytes + (size_t)q.n_w * wbytes;
-      su->grid = dim3((unsigned)std::min<long long>(tiles * best_d, sms));  // persistent: one CTA per SM
+      su->grid = dim3((unsigned)std::min<long long>(q.tail_start + (tiles - q.tail_tile0) * q.tail_d, sms));  // persistent: one CTA per SM
       su->in = in;
       su->shape = s;
       su->valid = true;
@@ -898,8 +1022,9 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
     cudaDeviceSynchronize();
     cudaMemcpy(h, d_prof, sizeof(h), cudaMemcpyDeviceToHost);
     const char *names[6] = {"x loader (xempty)", "w loader (gdone)", "cp (gdone-4, xconv)", "mma (afull, pempty, wfull; mmas, commit)", "convert (xfull)", "sum (gdone)"};
-    const long long items = ((long long)p.tiles_w * p.tiles_h * p.tiles_n * ((s.OC + bn - 1) / bn) * p.ksplit + grid.x - 1) / grid.x;
-    const long long steps = items * (long long)s.KS * s.KS * (p.n_chunks / p.ksplit);
+    const long long tiles_ = (long long)p.tiles_w * p.tiles_h * p.tiles_n * ((s.OC + bn - 1) / bn);
+    const long long items = (p.tail_start + (tiles_ - p.tail_tile0) * p.tail_d + grid.x - 1) / grid.x;
+    const long long steps = (long long)(p.tail_start / grid.x) * s.KS * s.KS * (p.n_chunks / p.ksplit) + (long long)s.KS * s.KS * (p.n_chunks / p.tail_d);
     fprintf(stderr, "[tc16 prof] grid %u, items/CTA %lld, K steps/CTA %lld, n_x %d n_w %d\n", grid.x, items, steps, p.n_x, p.n_w);
     for (int r = 0; r < 6; ++r)
       fprintf(stderr, "[tc16 prof] %-42s total %9lld clk (%5.0f per K step); waits: %lld %lld %lld %lld %lld\n", names[r], h[r * 8],
