@@ -478,3 +478,34 @@ def test_tensor16_against_tensor_many_shapes_and_repeats(tb, torch_cuda):
         torch.cuda.synchronize()
         f.check()
         assert agree(ref, y)
+
+
+@pytest.mark.parametrize("case", [(19, 64, 32, 32, 128, 3, 1), (20, 128, 28, 28, 128, 3, 1), (150, 96, 14, 14, 64, 3, 1),
+                                  (5, 64, 40, 40, 100, 1, 0)],
+                         ids=lambda c: "n%d_ic%d_%dx%d_oc%d_k%d" % c[:6])
+def test_tensor16_last_wave_split(tb, torch_cuda, oracle, case):
+    """Shapes whose tiles leave a small last wave on a 148-SM part, so that the split-FP16 variant
+    cuts those tiles into K slices and adds them up through its scratch blocks: results against
+    the oracle, rectified as well, and bit-identical from launch to launch (the slices are added
+    in slice order whoever finishes last)."""
+    torch = torch_cuda
+    n, ic, h, w, oc, ks, pad = case
+    rng = np.random.default_rng(4000 + n)
+    filt = rng.normal(0, 0.05, (oc, ic, ks, ks)).astype(np.float32)
+    filt[rng.random(filt.shape) < 0.8] = 0
+    x = rng.random((n, ic, h, w), dtype=np.float32) - 0.3
+    f = tb.SparseFilter(filt, ic, oc, ks)
+    want = oracle.host_conv2d(x, filt, 1, pad)
+    got = device_conv(tb, torch_cuda, f, x, 1, pad, VARIANTS["tensor16"])
+    check(oracle, got, want)
+    xin = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
+    oh, ow = want.shape[2], want.shape[3]
+    outs = []
+    for _ in range(3):
+        out = torch.full((n, oh, ow, oc), float("nan"), device="cuda")
+        tb.sparse_conv2d_fused(f, xin, out, n, h, w, 1, pad, variant=VARIANTS["tensor16"], relu=True)
+        torch.cuda.synchronize()
+        outs.append(out.cpu().numpy())
+    f.check()
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    assert oracle.compare(outs[0].transpose(0, 3, 1, 2), np.maximum(want, 0))[0] == 0
