@@ -37,12 +37,13 @@
 //     halo (4-D box, out-of-range coordinates zero-filled = the padding) into a ring of stages;
 //   * warps 4-7: convert a landed patch in place, one 128-byte row per thread, conflict-free;
 //   * warp 3 (one elected lane): per K step four tcgen05.cp (x_hi and x_lo, two K slices each)
-//     into one of four operand blocks; per PAIR of K steps one wait (the MMAs that read the block
-//     four pairs ago are done) and one commit;
-//   * warp 2 (one thread): one bulk copy per pair of K steps of prepared {w_hi, w_lo} tile images;
-//   * warp 1 (one elected lane): 6 tcgen05.mma per K step; per pair two waits (operands copied,
-//     weights landed) and one commit.  The pipeline's unit is a pair of K steps because a wait
-//     costs a warp ~200 clocks and a commit ~250, against ~450 for the pair's twelve MMAs;
+//     into one of the operand blocks; per GROUP of U K steps (U = 2, or 4 for 64-channel tiles
+//     under filters larger than 1x1) one wait (the MMAs that read the block a lap ago are done)
+//     and one commit;
+//   * warp 2 (one thread): one bulk copy per group of K steps of prepared {w_hi, w_lo} tile images;
+//   * warp 1 (one elected lane): 6 tcgen05.mma per K step; per group two waits (operands copied,
+//     weights landed) and one commit.  The pipeline's unit is a group of K steps because a wait
+//     costs a warp ~200 clocks and a commit ~250, against ~450 for the twelve MMAs of a pair;
 //   * warps 8-15: partial accumulators -> running sum in registers -> staged, coalesced stores.
 // Every barrier wait is bounded; on a timeout an error flag is raised, all roles drain, TMEM is
 // freed and the kernel returns; the host reports TETRIS_ERR_CUDA.
@@ -67,16 +68,16 @@ namespace {
 
 constexpr int BM = 128, KC = 32;         // tile rows (pixels); K chunk (32 channels)
 constexpr int kTW = 8, kTH = 16;         // a tile is 16 groups of 8 output columns
-constexpr int kAStages = 4;              // operand blocks in tensor memory: one per pair of K steps, 64 columns each
-constexpr int kACols = 64;               // per K step {x_hi k0, x_hi k1, x_lo k0, x_lo k1} x 8 columns
+constexpr int kAStagesMax = 4;           // operand blocks in tensor memory: one per group of U K steps, 256 / (32 U) of them
+constexpr int kStepCols = 32;            // per K step {x_hi k0, x_hi k1, x_lo k0, x_lo k1} x 8 columns
 constexpr int kTmemCols = 512;           // 2 partial accumulators (<= 128 columns each) + 8 x 32 operand columns
 constexpr int kTmemA = 256;
-constexpr int kWStagesMax = 4, kXStagesMax = 6;   // weight stages hold a pair of K steps
-constexpr int kGroups = 16;              // "pair done" barriers in rotation (a power of two, 2^4: see wait_pair)
-constexpr int kSuper = 4;                // pairs (8 K steps, 48 MMAs) accumulated on the tensor core before the FP32 add outside
+constexpr int kWStagesMax = 4, kXStagesMax = 6;   // weight stages hold a group of K steps
+constexpr int kGroups = 16;              // "group done" barriers in rotation (a power of two, 2^4: see wait_group)
+constexpr int kSuperSteps = 8;           // K steps (48 MMAs) accumulated on the tensor core before the FP32 add outside
 constexpr int kThreads = 512;            // warp 0 x loads, 1 MMA, 2 w loads, 3 cp, 4-7 convert, 8-15 sum + store
 constexpr int kStoreBytes = 8 * 4096;    // store staging: per summing warp 32 rows x 32 channels
-constexpr int kNumBars = 3 * kXStagesMax + kWStagesMax + kAStages + kGroups + 2;
+constexpr int kNumBars = 3 * kXStagesMax + kWStagesMax + kAStagesMax + kGroups + 2;
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kXScale = 16.f;          // activations are multiplied by this before the split (undone in out_scale)
 
@@ -182,14 +183,20 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
   return *reinterpret_cast<const uint32_t *>(&h);
 }
 
-template <int BN>
+// BN: output channels of a tile.  U: K steps per pipeline group -- the unit the copy warp and the
+// MMA warp wait, issue and commit by (2 for BN = 128; 4 for BN = 64, whose MMAs are short enough
+// that a wait and a commit per pair of steps would set the pace).
+template <int BN, int U>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char *xbase = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
   unsigned char *wbase = xbase + (size_t)p.n_x * p.x_stage_bytes;
-  constexpr int kWBytes = BN * 128;      // weights of one K step: BN rows of {w_hi (64 B), w_lo (64 B)}; a stage holds two
-  unsigned char *store_base = wbase + (size_t)p.n_w * 2 * kWBytes;
+  constexpr int kWBytes = BN * 128;      // weights of one K step: BN rows of {w_hi (64 B), w_lo (64 B)}; a stage holds U
+  constexpr int kAStages = 256 / (kStepCols * U);   // operand blocks in rotation (a power of two)
+  constexpr int kSuper = kSuperSteps / U;           // groups per partial sum
+  static_assert(kAStages <= kAStagesMax && kAStages * kStepCols * U == 256 && kSuper * U == kSuperSteps, "group size");
+  unsigned char *store_base = wbase + (size_t)p.n_w * U * kWBytes;
   uint64_t *bars = reinterpret_cast<uint64_t *>(store_base + kStoreBytes);
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -199,7 +206,7 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
   auto bar_xempty = [&](int s) { return smem_u32(&bars[2 * kXStagesMax + s]); };
   auto bar_wfull = [&](int s) { return smem_u32(&bars[3 * kXStagesMax + s]); };
   auto bar_afull = [&](int s) { return smem_u32(&bars[3 * kXStagesMax + kWStagesMax + s]); };
-  auto bar_gdone = [&](int c) { return smem_u32(&bars[3 * kXStagesMax + kWStagesMax + kAStages + c]); };
+  auto bar_gdone = [&](int c) { return smem_u32(&bars[3 * kXStagesMax + kWStagesMax + kAStagesMax + c]); };
   auto bar_pempty = [&](int b) { return smem_u32(&bars[kNumBars - 2 + b]); };
 
   if (tid == 0) {
@@ -243,9 +250,9 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
   const int total_tiles = p.tiles_w * p.tiles_h * p.tiles_n * oc_tiles;
   const int total_items = p.tail_start + (total_tiles - p.tail_tile0) * p.tail_d;
   // A work item is a tile, or one of ksplit equal slices of a tile's K range (all tiles), or --
-  // for the tiles of the last wave -- one of tail_d slices.  The pipeline's unit is a PAIR of K
-  // steps (the last of an item may be single).
-  struct Item { int tile, chunk0, chunks, iters, npairs, supers; bool tail; int slice; };
+  // for the tiles of the last wave -- one of tail_d slices.  The pipeline's unit is a GROUP of U K
+  // steps (the last of an item may be shorter).
+  struct Item { int tile, chunk0, chunks, iters, ngroups, supers; bool tail; int slice; };
   auto item_of = [&](int t) {
     Item it;
     it.tail = t >= p.tail_start;
@@ -255,8 +262,8 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
     it.chunks = p.n_chunks / d;
     it.chunk0 = it.slice * it.chunks;
     it.iters = taps * it.chunks;
-    it.npairs = (it.iters + 1) / 2;
-    it.supers = (it.npairs + kSuper - 1) / kSuper;
+    it.ngroups = (it.iters + U - 1) / U;
+    it.supers = (it.ngroups + kSuper - 1) / kSuper;
     return it;
   };
   auto decode = [&](int t, int &w0, int &h0, int &n0, int &oc0) {
@@ -265,11 +272,11 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
     h0 = (t % p.tiles_h) * p.TH;
     n0 = (t / p.tiles_h) * p.NB;
   };
-  // Pair G of this CTA (counted across work items) signals bar_gdone(G % kGroups) when its MMAs
-  // have completed.  Nobody looks at a pair's barrier later than 16 pairs after it: the rings are
-  // 4 pairs deep and the MMAs run at most two partial sums (8 pairs) ahead of the summing warps.
-  auto wait_pair = [&](int G) { return mbar_wait(bar_gdone(G & (kGroups - 1)), (G >> 4) & 1, abort_flag); };
-  auto wait_pair_warp = [&](int G) { return mbar_wait_warp(bar_gdone(G & (kGroups - 1)), (G >> 4) & 1, abort_flag); };
+  // Group G of this CTA (counted across work items) signals bar_gdone(G % kGroups) when its MMAs
+  // have completed.  Nobody looks at a group's barrier later than 16 groups after it: the rings are
+  // at most 4 groups deep and the MMAs run at most two partial sums (8 groups) ahead of the summing warps.
+  auto wait_group = [&](int G) { return mbar_wait(bar_gdone(G & (kGroups - 1)), (G >> 4) & 1, abort_flag); };
+  auto wait_group_warp = [&](int G) { return mbar_wait_warp(bar_gdone(G & (kGroups - 1)), (G >> 4) & 1, abort_flag); };
 
   if (warp == 0) {
     // ---- activation loads: one patch (tile + halo) per 32-channel chunk ----
@@ -298,23 +305,23 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
       PROF_OUT(0);
     }
   } else if (warp == 2) {
-    // ---- weight loads: one bulk copy per pair (the {w_hi, w_lo} images of its K steps lie
+    // ---- weight loads: one bulk copy per group (the {w_hi, w_lo} images of its K steps lie
     //      back to back in global memory) ----
     if (lane == 0) {
       int G = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
         const Item it = item_of(t);
-        const int iters = it.iters, npairs = it.npairs;
+        const int iters = it.iters, ngroups = it.ngroups;
         int w0, h0, n0, oc0;
         decode(it.tile, w0, h0, n0, oc0);
         const __half *item = p.w_tiles + ((size_t)(oc0 / BN) * p.n_chunks + it.chunk0) * taps * (size_t)(BN * 64);
-        for (int j = 0; j < npairs; ++j, ++G) {
+        for (int j = 0; j < ngroups; ++j, ++G) {
           const int s = G % p.n_w;
-          if (G >= p.n_w && !(ok = TIMED(0, wait_pair(G - p.n_w)))) break;
-          const uint32_t bytes = (uint32_t)(min(2, iters - 2 * j) * kWBytes);
+          if (G >= p.n_w && !(ok = TIMED(0, wait_group(G - p.n_w)))) break;
+          const uint32_t bytes = (uint32_t)(min(U, iters - U * j) * kWBytes);
           mbar_expect_tx(bar_wfull(s), bytes);
-          bulk_load(smem_u32(wbase + (size_t)s * 2 * kWBytes), item + (size_t)(2 * j) * (BN * 64), bytes, bar_wfull(s));
+          bulk_load(smem_u32(wbase + (size_t)s * U * kWBytes), item + (size_t)(U * j) * (BN * 64), bytes, bar_wfull(s));
         }
       }
       PROF_OUT(1);
@@ -339,56 +346,52 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
       int r = 0, q = 0;  // tap of the next K step
       // flat mode: the tile's first position lies (P0 mod PW) rows into its first padded row
       const Item it = item_of(t);
-      const int iters = it.iters, npairs = it.npairs;
+      const int iters = it.iters, ngroups = it.ngroups;
       uint32_t td0 = 0;
       if (p.flat) {
         const int P0 = ((it.tile / oc_tiles) % p.tiles_w) * BM;
         td0 = (uint32_t)((P0 - (P0 / p.PW) * p.PW) * 8);
       }
       td = td0;
-      for (int j = 0; j < npairs; ++j, ++G) {
+      for (int j = 0; j < ngroups; ++j, ++G) {
         const int sa = G & (kAStages - 1);
-        const bool two = iters - 2 * j >= 2;
-        // the MMAs that read this operand block (four pairs ago) are done
-        if (G >= kAStages && !(ok = TIMED(0, wait_pair_warp(G - kAStages)))) break;
-        // the patch of the pair's first K step is converted (waited for once per patch); that of
-        // the second step, when it is the next patch, below
-        if (fresh_patch) {
-          if (!(ok = TIMED(1, mbar_wait_warp(bar_xconv(sx), xphase, abort_flag)))) break;
-          fresh_patch = false;
+        const int ns = min(U, iters - U * j);
+        // the MMAs that read this operand block (kAStages groups ago) are done
+        if (G >= kAStages && !(ok = TIMED(0, wait_group_warp(G - kAStages)))) break;
+        // per step: the window of its tap in the converted patch (waited for once per patch), and
+        // the barrier that releases the patch if this step is its last
+        uint32_t a[U], freed[U];
+#pragma unroll
+        for (int e = 0; e < U; ++e) {
+          a[e] = 0; freed[e] = 0;
+          if (e < ns && ok) {
+            if (fresh_patch) {
+              ok = TIMED(1, mbar_wait_warp(bar_xconv(sx), xphase, abort_flag));
+              fresh_patch = false;
+            }
+            a[e] = xd + td;
+            if (r == p.KS - 1 && q == p.KS - 1) {
+              freed[e] = bar_xempty(sx);
+              r = 0; q = 0; td = td0; fresh_patch = true;
+              if (++sx == p.n_x) { sx = 0; xd = x0; xphase ^= 1u; } else xd += stage_step;
+            }
+            else if (++q == p.KS) { q = 0; ++r; td += row_step; }
+            else td += 8;
+          }
         }
-        if (two && r == p.KS - 1 && q == p.KS - 1) {  // the second step opens the next patch
-          const int nsx = sx + 1 == p.n_x ? 0 : sx + 1;
-          if (!(ok = TIMED(1, mbar_wait_warp(bar_xconv(nsx), nsx == 0 ? xphase ^ 1u : xphase, abort_flag)))) break;
-        }
+        if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t ta = tmem_base + (uint32_t)(kTmemA + sa * kACols), t1 = ta + 32u;
-        const uint32_t a0 = xd + td;
-        const int sx0 = sx;
-        const bool last0 = r == p.KS - 1 && q == p.KS - 1;
-        if (last0) { r = 0; q = 0; td = td0; if (++sx == p.n_x) { sx = 0; xd = x0; xphase ^= 1u; } else xd += stage_step; }
-        else if (++q == p.KS) { q = 0; ++r; td += row_step; }
-        else td += 8;
-        const uint32_t a1 = xd + td;
-        const int sx1 = sx;
-        const bool last1 = two && r == p.KS - 1 && q == p.KS - 1;
-        if (two) {
-          if (last1) { r = 0; q = 0; td = td0; if (++sx == p.n_x) { sx = 0; xd = x0; xphase ^= 1u; } else xd += stage_step; }
-          else if (++q == p.KS) { q = 0; ++r; td += row_step; }
-          else td += 8;
-        }
-        // a step that was the last of its patch leaves the next patch unwaited-for -- unless the
-        // pair's second step already opened (and waited for) it
-        if (last1) fresh_patch = true;
-        else if (last0) fresh_patch = !two;
+        const uint32_t ta = tmem_base + (uint32_t)(kTmemA + sa * (kStepCols * U));
         if (elect_one()) {
           // operand block of a K step: columns 0-7 / 8-15 x_hi of channels 0-15 / 16-31, 16-23 / 24-31 x_lo
           // (32 bytes along K = 2 in a descriptor's address field)
-          tmem_cp(ta, a0, da_hi); tmem_cp(ta + 8, a0 + 2, da_hi); tmem_cp(ta + 16, a0 + 4, da_hi); tmem_cp(ta + 24, a0 + 6, da_hi);
-          if (last0) umma_commit(bar_xempty(sx0));  // the patch has been read for the last time
-          if (two) {
-            tmem_cp(t1, a1, da_hi); tmem_cp(t1 + 8, a1 + 2, da_hi); tmem_cp(t1 + 16, a1 + 4, da_hi); tmem_cp(t1 + 24, a1 + 6, da_hi);
-            if (last1) umma_commit(bar_xempty(sx1));
+#pragma unroll
+          for (int e = 0; e < U; ++e) {
+            if (e < ns) {
+              const uint32_t te = ta + (uint32_t)(e * kStepCols);
+              tmem_cp(te, a[e], da_hi); tmem_cp(te + 8, a[e] + 2, da_hi); tmem_cp(te + 16, a[e] + 4, da_hi); tmem_cp(te + 24, a[e] + 6, da_hi);
+              if (freed[e]) umma_commit(freed[e]);  // the patch has been read for the last time
+            }
           }
           umma_commit(bar_afull(sa));
         }
@@ -398,7 +401,7 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
     PROF_OUT(2);
   } else if (warp == 1) {
     // ---- MMA issue (converged warp, one elected lane): six tcgen05.mma per K step, one wait and
-    //      one commit per pair ----
+    //      one commit per group ----
     const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     const uint32_t dw_hi = (uint32_t)(smem_desc(0, 1024) >> 32);
     const uint32_t w0 = (uint32_t)smem_desc(smem_u32(wbase), 1024);
@@ -407,41 +410,39 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
     bool ok = true;
     for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
       const Item it = item_of(t);
-      const int iters = it.iters, npairs = it.npairs;
+      const int iters = it.iters, ngroups = it.ngroups;
       const int sbase0 = sbase;
       sbase += it.supers;
-      for (int j = 0, jj = 0, si = 0; j < npairs; ++j, ++G) {
+      for (int j = 0, jj = 0, si = 0; j < ngroups; ++j, ++G) {
         const int sa = G & (kAStages - 1);
         const uint32_t acc0 = jj == 0 ? 0u : 1u;  // the first MMA of a partial overwrites it
         const uint32_t tmem_d = tmem_base + (uint32_t)(((sbase0 + si) & 1) * BN);
-        if (jj == 0) {  // first pair of a partial sum: its accumulator has been drained (two partials ago)
+        if (jj == 0) {  // first group of a partial sum: its accumulator has been drained (two partials ago)
           if (!(ok = TIMED(1, mbar_wait_warp(bar_pempty(sp & 1), ((sp >> 1) & 1) ^ 1, abort_flag)))) break;
           ++sp;
         }
         if (++jj == kSuper) { jj = 0; ++si; }
-        if (!(ok = TIMED(2, mbar_wait_warp(bar_wfull(sw), wphase, abort_flag)))) break;  // the pair's weights have landed
-        if (!(ok = TIMED(0, mbar_wait_warp(bar_afull(sa), (G >> 2) & 1, abort_flag)))) break;  // ... and its operand blocks
+        if (!(ok = TIMED(2, mbar_wait_warp(bar_wfull(sw), wphase, abort_flag)))) break;  // the group's weights have landed
+        if (!(ok = TIMED(0, mbar_wait_warp(bar_afull(sa), (G / kAStages) & 1, abort_flag)))) break;  // ... and its operand blocks
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         PROF_START();
-        const bool two = iters - 2 * j >= 2;
-        const uint32_t ta = tmem_base + (uint32_t)(kTmemA + sa * kACols), t1 = ta + 32u;
-        const uint32_t dlo = wd, d1 = wd + (uint32_t)(kWBytes >> 4);
-        if (++sw == p.n_w) { sw = 0; wd = w0; wphase ^= 1u; } else wd += (uint32_t)(2 * kWBytes >> 4);
+        const int ns = min(U, iters - U * j);
+        const uint32_t ta = tmem_base + (uint32_t)(kTmemA + sa * (kStepCols * U));
+        const uint32_t dlo = wd;
+        if (++sw == p.n_w) { sw = 0; wd = w0; wphase ^= 1u; } else wd += (uint32_t)(U * kWBytes >> 4);
         if (elect_one()) {
           // K slices of 16 channels: 32 bytes = 2 in the address field; w_lo sits 64 bytes after w_hi
-          umma_f16_ts(tmem_d, ta, dlo, dw_hi, idesc, acc0);
-          umma_f16_ts(tmem_d, ta + 16, dlo, dw_hi, idesc, 1u);
-          umma_f16_ts(tmem_d, ta, dlo + 4, dw_hi, idesc, 1u);
-          umma_f16_ts(tmem_d, ta + 8, dlo + 2, dw_hi, idesc, 1u);
-          umma_f16_ts(tmem_d, ta + 24, dlo + 2, dw_hi, idesc, 1u);
-          umma_f16_ts(tmem_d, ta + 8, dlo + 6, dw_hi, idesc, 1u);
-          if (two) {
-            umma_f16_ts(tmem_d, t1, d1, dw_hi, idesc, 1u);
-            umma_f16_ts(tmem_d, t1 + 16, d1, dw_hi, idesc, 1u);
-            umma_f16_ts(tmem_d, t1, d1 + 4, dw_hi, idesc, 1u);
-            umma_f16_ts(tmem_d, t1 + 8, d1 + 2, dw_hi, idesc, 1u);
-            umma_f16_ts(tmem_d, t1 + 24, d1 + 2, dw_hi, idesc, 1u);
-            umma_f16_ts(tmem_d, t1 + 8, d1 + 6, dw_hi, idesc, 1u);
+#pragma unroll
+          for (int e = 0; e < U; ++e) {
+            if (e < ns) {
+              const uint32_t te = ta + (uint32_t)(e * kStepCols), de = dlo + (uint32_t)(e * (kWBytes >> 4));
+              umma_f16_ts(tmem_d, te, de, dw_hi, idesc, e == 0 ? acc0 : 1u);
+              umma_f16_ts(tmem_d, te + 16, de, dw_hi, idesc, 1u);
+              umma_f16_ts(tmem_d, te, de + 4, dw_hi, idesc, 1u);
+              umma_f16_ts(tmem_d, te + 8, de + 2, dw_hi, idesc, 1u);
+              umma_f16_ts(tmem_d, te + 24, de + 2, dw_hi, idesc, 1u);
+              umma_f16_ts(tmem_d, te + 8, de + 6, dw_hi, idesc, 1u);
+            }
           }
           PROF_LAP(3);
           umma_commit(bar_gdone(G & (kGroups - 1)));
@@ -525,19 +526,19 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
         pix = ((size_t)n * p.OH + oh) * p.OW + ow;
       }
     };
-    int gbase = 0, sp = 0;  // first pair of the item; partial sum, counted across items
+    int gbase = 0, sp = 0;  // first group of the item; partial sum, counted across items
     bool ok = true;
     for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
-      int npairs, tile_supers;
-      { const Item head = item_of(t); npairs = head.npairs; tile_supers = head.supers; }
+      int ngroups, tile_supers;
+      { const Item head = item_of(t); ngroups = head.ngroups; tile_supers = head.supers; }
       const int gbase0 = gbase;
-      gbase += npairs;
+      gbase += ngroups;
       float acc[NC];
 #pragma unroll
       for (int j = 0; j < NC; ++j) acc[j] = 0.f;
       for (int si = 0; si < tile_supers; ++si, ++sp) {
         const int b = sp & 1;
-        if (!(ok = TIMED(0, wait_pair_warp(gbase0 + min((si + 1) * kSuper, npairs) - 1)))) break;  // the partial's last pair
+        if (!(ok = TIMED(0, wait_group_warp(gbase0 + min((si + 1) * kSuper, ngroups) - 1)))) break;  // the partial's last group
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + half * NC);
 #pragma unroll
@@ -842,6 +843,12 @@ int conv_tc16_prepare(tetris_filter *f, const float *d_dense) {
   return TETRIS_OK;
 }
 
+// K steps per pipeline group of the kernel instance that serves channel tiles of `bn` and filters
+// of `ks` x `ks`: four for 64-channel tiles, whose MMAs are short (measured on VGG-19 conv1_2 and
+// the 64-channel 3x3 layers of ResNet-50: 3-4 % faster than pairs); 1x1 filters, where a group of
+// four would wait for four patches at a time, and 128-channel tiles stay with pairs.
+static int group_steps(int bn, int ks) { return bn == 64 && ks > 1 ? 4 : 2; }
+
 bool conv_tc16_supported(const tetris_filter *f, const ConvShape &s) {
   if (!f->tc16_state || !f->tc_state || f->groups != 1) return false;  // (the split-TF32 variant is the out-of-range fallback)
   if (s.S != 1 || s.N < 1 || s.OH < 1 || s.OW < 1 || (s.IC & 3) != 0) return false;
@@ -965,12 +972,12 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
         if (rest > 0 && d >= 2) { q.tail_tile0 = full; q.tail_start = full; q.tail_d = d; }
       }
       // shared memory: activation ring, weight ring, store staging, barriers
-      const size_t wbytes = (size_t)t->bn * 128 * 2;  // a weight stage holds a pair of K steps
+      const size_t wbytes = (size_t)t->bn * 128 * group_steps(t->bn, KS);  // a weight stage holds a group of K steps
       const size_t fixed = 1024 + kStoreBytes + kNumBars * 8 + 16;
       const int chunks_per_item = q.n_chunks / best_d;
       q.n_w = kWStagesMax;
       q.n_x = (int)std::min<size_t>(kXStagesMax, (kSmemBudget - fixed - q.n_w * wbytes) / q.x_stage_bytes);
-      while (q.n_x < 3 && q.n_w > 3) {  // (a pair of K steps may straddle two patches: at least two stages, better three)
+      while (q.n_x < 3 && q.n_w > 3) {  // (a group of K steps may straddle two patches: at least two stages, better three)
         --q.n_w;
         q.n_x = (int)std::min<size_t>(kXStagesMax, (kSmemBudget - fixed - q.n_w * wbytes) / q.x_stage_bytes);
       }
@@ -1003,16 +1010,19 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
   int dev = 0;
   TETRIS_CUDA_TRY(cudaGetDevice(&dev));
   if (dev >= 16 || !configured[dev]) {
-    TETRIS_CUDA_TRY(cudaFuncSetAttribute(conv_tc16_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-    TETRIS_CUDA_TRY(cudaFuncSetAttribute(conv_tc16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    TETRIS_CUDA_TRY(cudaFuncSetAttribute(conv_tc16_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    TETRIS_CUDA_TRY(cudaFuncSetAttribute(conv_tc16_kernel<64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    TETRIS_CUDA_TRY(cudaFuncSetAttribute(conv_tc16_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
     if (dev < 16) configured[dev] = true;
   }
   if (p.ksplit > 1)  // the work items add into the output
     TETRIS_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)s.N * s.OH * s.OW * s.OC * sizeof(float), st));
-  if (bn == 64)
-    conv_tc16_kernel<64><<<grid, kThreads, smem, st>>>(map_x, p);
+  if (bn == 64 && group_steps(64, s.KS) == 4)
+    conv_tc16_kernel<64, 4><<<grid, kThreads, smem, st>>>(map_x, p);
+  else if (bn == 64)
+    conv_tc16_kernel<64, 2><<<grid, kThreads, smem, st>>>(map_x, p);
   else
-    conv_tc16_kernel<128><<<grid, kThreads, smem, st>>>(map_x, p);
+    conv_tc16_kernel<128, 2><<<grid, kThreads, smem, st>>>(map_x, p);
   TETRIS_CUDA_TRY(cudaGetLastError());
   count_launch();
   if (p.relu) note_relu_fused();
