@@ -324,6 +324,21 @@ int tetris_filter_file_check(const char *path, tetris_filter_info_t *info);
  */
 unsigned long long tetris_launch_count(void);
 
+/*
+ * Failure-detection test hook (no counterpart in the reference, whose kernels have no waits that
+ * can fail).  Every barrier wait inside the tensor-core kernels is bounded; when one runs out the
+ * kernel raises a flag, lets every role drain (loads, copies and MMAs already started are waited
+ * for), frees its tensor memory and returns, and tetris_filter_check reports TETRIS_ERR_CUDA once.
+ * tetris_test_inject(TETRIS_INJECT_WITHHOLD_LOAD, n) makes the following tensor-core launches of
+ * this process leave out every CTA's first activation load and give up after n polls (0: the
+ * built-in limit, seconds), so that a test can see that path end to end without a GPU fault: the
+ * launch returns normally, its output is unspecified, the context stays usable.
+ * tetris_test_inject(TETRIS_INJECT_NONE, 0) switches it off.  Never use it outside tests.
+ */
+#define TETRIS_INJECT_NONE 0
+#define TETRIS_INJECT_WITHHOLD_LOAD 1
+int tetris_test_inject(int what, unsigned spin_limit);
+
 /* Text of the last error raised on this thread ("" if none). */
 const char *tetris_last_error(void);
 

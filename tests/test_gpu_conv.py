@@ -509,3 +509,45 @@ def test_tensor16_last_wave_split(tb, torch_cuda, oracle, case):
     f.check()
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
     assert oracle.compare(outs[0].transpose(0, 3, 1, 2), np.maximum(want, 0))[0] == 0
+
+
+@pytest.mark.parametrize("variant", ["tensor", "tensor16"])
+def test_bounded_wait_gives_up_and_the_next_launch_passes(tb, torch_cuda, oracle, variant):
+    """Failure detection without a GPU fault: with every CTA's first activation load left out
+    (tetris_test_inject) a barrier wait of the tensor-core kernel runs out after a short poll
+    limit; the launch returns normally, tetris_filter_check reports TETRIS_ERR_CUDA exactly once,
+    the context stays usable, and the next launch of the same filter matches the oracle.  (The
+    reference kernels have no waits that can fail; the give-up path guards this design's
+    producer/consumer pipeline.)"""
+    torch = torch_cuda
+    rng = np.random.default_rng(4242)
+    n, ic, h, w, oc, ks, pad = 2, 64, 24, 24, 128, 3, 1
+    filt = (rng.standard_normal((oc, ic, ks, ks)) * (rng.random((oc, ic, ks, ks)) >= 0.8)).astype(np.float32)
+    x = rng.random((n, ic, h, w), dtype=np.float32)
+    want = oracle.host_conv2d(x, filt, 1, pad, threads=True, skip_zero=True)
+    f = tb.SparseFilter(filt, ic, oc, ks)
+    xin = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
+    out = torch.full((n, h, w, oc), float("nan"), device="cuda")
+    v = VARIANTS[variant]
+    tb.sparse_conv2d(f, xin, out, n, h, w, 1, pad, variant=v)
+    torch.cuda.synchronize()
+    f.check()
+    tb.test_inject(1, 2048)
+    try:
+        tb.sparse_conv2d(f, xin, out, n, h, w, 1, pad, variant=v)   # returns; its output is unspecified
+        torch.cuda.synchronize()                                    # no CUDA error: the kernel gave up by itself
+        with pytest.raises(tb.TetrisError) as err:
+            f.check()
+        assert err.value.status == 2, err.value                     # TETRIS_ERR_CUDA
+    finally:
+        tb.test_inject(0)
+    f.check()                                                       # reported once, then cleared
+    out.fill_(float("nan"))
+    tb.sparse_conv2d(f, xin, out, n, h, w, 1, pad, variant=v)
+    torch.cuda.synchronize()
+    f.check()
+    got = out.cpu().numpy().transpose(0, 3, 1, 2)
+    assert not np.isnan(got).any()
+    bad, max_rel, _ = oracle.compare(got, want)
+    assert bad == 0, "%d elements differ after the recovery (max rel %.3g)" % (bad, max_rel)
+    f.close()

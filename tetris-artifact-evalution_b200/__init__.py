@@ -92,6 +92,7 @@ SIGNATURES = {
     "tetris_filter_load": (_I, [ctypes.c_char_p, _I, ctypes.POINTER(_VP)]),
     "tetris_filter_file_check": (_I, [ctypes.c_char_p, ctypes.POINTER(FilterInfo)]),
     "tetris_launch_count": (ctypes.c_ulonglong, []),
+    "tetris_test_inject": (ctypes.c_int, [ctypes.c_int, ctypes.c_uint]),
     "tetris_last_error": (ctypes.c_char_p, []),
 }
 
@@ -421,6 +422,12 @@ def filter_file_check(path):
 def launch_count():
     """Convolution kernels launched through the library by this process so far."""
     return int(lib().tetris_launch_count())
+
+
+def test_inject(what, spin_limit=0):
+    """Failure-detection test hook (tetris_test_inject): 1 = the tensor-core kernels leave out every
+    CTA's first activation load and their barrier waits give up after `spin_limit` polls; 0 = off."""
+    _check(lib().tetris_test_inject(int(what), int(spin_limit)))
 
 
 def batch_slice(batch_size, world, rank):

@@ -19,6 +19,13 @@ static thread_local char g_error[512] = "";
 static std::atomic<unsigned long long> g_launches{0};
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+static std::atomic<int> g_inject{0};
+static std::atomic<unsigned> g_inject_spin{0};
+int test_injection(unsigned *spin_limit) {
+  const int what = g_inject.load(std::memory_order_relaxed);
+  *spin_limit = what ? g_inject_spin.load(std::memory_order_relaxed) : 0u;
+  return what == TETRIS_INJECT_WITHHOLD_LOAD ? 1 : 0;
+}
 
 void set_error(const char *fmt, ...) {
   va_list ap;
@@ -128,6 +135,16 @@ extern "C" {
 const char *tetris_last_error(void) { return g_error; }
 
 unsigned long long tetris_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int tetris_test_inject(int what, unsigned spin_limit) {
+  if (what != TETRIS_INJECT_NONE && what != TETRIS_INJECT_WITHHOLD_LOAD) {
+    tetris::set_error("tetris_test_inject: unknown injection %d", what);
+    return TETRIS_ERR_INVALID;
+  }
+  tetris::g_inject_spin.store(spin_limit, std::memory_order_relaxed);
+  tetris::g_inject.store(what, std::memory_order_relaxed);
+  return TETRIS_OK;
+}
 
 int tetris_filter_create(const float *filter_oihw, int in_channel, int out_channel,
                          int kernel_size, int groups, int device, tetris_filter_t **out) {

@@ -96,7 +96,7 @@ constexpr int kTmemCols = 512;              // 2 partial accumulators (<= 128 co
 constexpr int kTmemA = 256;                 // first operand column
 constexpr int kGroups = 8;                  // "group done" barriers in rotation (a group = kPromote K steps)
 constexpr int kThreads = 640;               // warp 0 x loads, 1 MMA, 2 w loads, 4-11 convert, 12-19 sum + store
-constexpr int kNumBars = 2 * kXStages + kWStages + 2 * kAStages + kGroups + 2;
+constexpr int kNumBars = 2 * kXStages + kWStages + 2 * kAStages + kGroups + 1 + 2;   // (... + one drain barrier + two partial-sum barriers)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct TcParams {
@@ -116,6 +116,8 @@ struct TcParams {
   int relu;                    // max(y, 0) at the store (never together with a split K range)
   int *error_flag;
   const float *w_tiles;        // weight tile images, see tc_weight_tiles_kernel
+  unsigned spin_limit;         // polls after which a barrier wait gives up (0: kSpinLimit)
+  int withhold_first_load;     // failure-detection test only: every CTA leaves out its first activation load
   unsigned *gate;              // when set: the launch runs only if the magnitude in gate[0] asks for it (see launch_conv_tc_gated)
 };
 
@@ -135,9 +137,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait.  Gives up when the limit is hit or when another role already gave up.
+// Bounded wait.  Gives up when the limit (abort_flag[1]) is hit or when another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint32_t limit = (uint32_t)abort_flag[1];
+  for (uint32_t i = 1; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63) == 63) {
       if (*abort_flag) return false;
@@ -146,6 +150,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   *abort_flag = 1;
   return false;
+}
+// After a give-up: wait (bounded, whatever the abort flag says) for an asynchronous operation this
+// thread started earlier, so that the CTA does not leave while a copy into its shared memory or
+// an MMA on its tensor memory is still in flight.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (1u << 16); ++i) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((i & 63) == 63) __nanosleep(64);
+  }
 }
 // The same for a whole converged warp, with one answer for all lanes.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int lane) {
@@ -240,6 +253,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
   auto bar_ready = [&](int s) { return smem_u32(&bars[2 * kXStages + kWStages + kAStages + s]); };
   auto bar_gdone = [&](int c) { return smem_u32(&bars[2 * kXStages + kWStages + 2 * kAStages + c]); };
   auto bar_pempty = [&](int b) { return smem_u32(&bars[kNumBars - 2 + b]); };
+  auto bar_drain = [&]() { return smem_u32(&bars[kNumBars - 3]); };
 
   if (tid == 0) {
     // a patch is read by all eight converter warps, a per-tap box by the four that take its K step
@@ -248,7 +262,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     for (int s = 0; s < kAStages; ++s) { mbar_init(bar_afull(s), 4); mbar_init(bar_ready(s), 1); }
     for (int c = 0; c < kGroups; ++c) mbar_init(bar_gdone(c), 1);
     for (int b = 0; b < 2; ++b) mbar_init(bar_pempty(b), 8);
-    *abort_flag = 0;
+    mbar_init(bar_drain(), 1);
+    abort_flag[0] = 0;
+    abort_flag[1] = (int)(p.spin_limit ? p.spin_limit : kSpinLimit);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // the whole tensor memory of the SM: this kernel runs one CTA per SM
@@ -307,10 +323,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           for (int chunk = chunk0; chunk < chunk0 + item_chunks; ++chunk, ++u) {
             const int s = u & 1;
             if (!(ok = mbar_wait(bar_xempty(s), ((u >> 1) & 1) ^ 1, abort_flag))) break;
+            if (u == 0 && p.withhold_first_load) continue;  // (test: this patch never arrives, its readers give up)
             mbar_expect_tx(bar_xfull(s), x_box_bytes);
             tma_load_4d(smem_u32(xbase + s * kPatchBytes), &map_x, bar_xfull(s), chunk * KC, w0 - p.P, h0 - p.P, n0);
           }
         }
+        if (!ok || *abort_flag)  // the loads of the last lap may still be in flight
+          for (int v = max(u - 2, p.withhold_first_load ? 1 : 0); v < u; ++v) mbar_drain(bar_xfull(v & 1), (uint32_t)(v >> 1) & 1u);
       } else {
         // Stride > 1: one box per K step, the tile's input pixels of that tap (every S-th
         // pixel; the tensor map carries the element strides).
@@ -321,12 +340,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           for (int it = 0; it < iters; ++it, ++u) {
             const int s = u % kXStages;
             if (!(ok = mbar_wait(bar_xempty(s), ((u / kXStages) & 1) ^ 1, abort_flag))) break;
+            if (u == 0 && p.withhold_first_load) continue;
             const int chunk = it / taps, tap = it - chunk * taps;
             const int r = tap / p.KS, q = tap - r * p.KS;
             mbar_expect_tx(bar_xfull(s), x_box_bytes);
             tma_load_4d(smem_u32(xbase + s * kTileBytes), &map_x, bar_xfull(s), (chunk0 + chunk) * KC, w0 * p.S + q - p.P, h0 * p.S + r - p.P, n0);
           }
         }
+        if (!ok || *abort_flag)
+          for (int v = max(u - kXStages, p.withhold_first_load ? 1 : 0); v < u; ++v) mbar_drain(bar_xfull(v % kXStages), (uint32_t)(v / kXStages) & 1u);
       }
     }
   } else if (warp == 2) {
@@ -346,6 +368,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           bulk_load(smem_u32(wbase + s * 2 * kTileBytes), src, (uint32_t)(2 * BN * KC * 4), bar_wfull(s));
         }
       }
+      if (!ok || *abort_flag)  // the copies of the last lap may still be in flight
+        for (int v = max(g - p.w_stages, 0); v < g; ++v) mbar_drain(bar_wfull(v % p.w_stages), (uint32_t)(v / p.w_stages) & 1u);
     }
   } else if (warp == 1) {
     // ---- MMA issue.  The whole warp runs the loop converged and one elected lane issues, so
@@ -386,6 +410,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
         if (ok && elect_one()) umma_commit(bar_gdone(c % kGroups));  // arrives when the group's last MMA has completed
         __syncwarp();
       }
+    }
+    if (!ok || *abort_flag) {  // the MMAs issued so far may still be running
+      if (elect_one()) umma_commit(bar_drain());
+      __syncwarp();
+      mbar_drain(bar_drain(), 0);
     }
   } else if (warp == 3) {
     // ---- gatekeeper (one thread): collects, per K step, the conditions under which the
@@ -939,6 +968,7 @@ int launch_conv_tc_impl(const tetris_filter *f, const float *in, float *out, con
   p.out = out;
   p.in = in;
   p.gate = gate;
+  p.withhold_first_load = test_injection(&p.spin_limit);
   const size_t smem = (size_t)kSmemTiles + 1024 + kNumBars * 8 + 16;
   static thread_local bool configured[16] = {false};
   int dev = 0;

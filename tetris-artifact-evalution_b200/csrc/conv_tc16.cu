@@ -77,7 +77,7 @@ constexpr int kGroups = 16;              // "group done" barriers in rotation (a
 constexpr int kSuperSteps = 8;           // K steps (48 MMAs) accumulated on the tensor core before the FP32 add outside
 constexpr int kThreads = 512;            // warp 0 x loads, 1 MMA, 2 w loads, 3 cp, 4-7 convert, 8-15 sum + store
 constexpr int kStoreBytes = 8 * 4096;    // store staging: per summing warp 32 rows x 32 channels
-constexpr int kNumBars = 3 * kXStagesMax + kWStagesMax + kAStagesMax + kGroups + 2;
+constexpr int kNumBars = 3 * kXStagesMax + kWStagesMax + kAStagesMax + kGroups + 2 + 2;   // (... + two drain barriers + two partial-sum barriers)
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kXScale = 16.f;          // activations are multiplied by this before the split (undone in out_scale)
 
@@ -107,6 +107,8 @@ struct Tc16Params {
   int *error_flag;
   unsigned *gate;              // gate[0]: largest |activation| of the launch, as FP32 bits (see launch_conv_tc_gated)
   const __half *w_tiles;
+  unsigned spin_limit;         // polls after which a barrier wait gives up (0: kSpinLimit)
+  int withhold_first_load;     // failure-detection test only: every CTA leaves out its first activation load
   long long *prof;             // per-role clock totals of CTA 0 for TETRIS_TC16_PROF=1 (nullptr = off)
 };
 
@@ -126,9 +128,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait.  Gives up when the limit is hit or when another role already gave up.
+// Bounded wait.  Gives up when the limit (abort_flag[1]) is hit or when another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint32_t limit = (uint32_t)abort_flag[1];
+  for (uint32_t i = 1; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63) == 63) {
       if (*abort_flag) return false;
@@ -140,6 +144,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
+// After a give-up: wait (bounded, whatever the abort flag says) for an asynchronous operation this
+// thread started earlier, so that the CTA does not leave while a copy into its shared memory or
+// an MMA on its tensor memory is still in flight.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (1u << 16); ++i) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((i & 63) == 63) __nanosleep(64);
+  }
 }
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3) {
   asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
@@ -208,14 +221,16 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
   auto bar_afull = [&](int s) { return smem_u32(&bars[3 * kXStagesMax + kWStagesMax + s]); };
   auto bar_gdone = [&](int c) { return smem_u32(&bars[3 * kXStagesMax + kWStagesMax + kAStagesMax + c]); };
   auto bar_pempty = [&](int b) { return smem_u32(&bars[kNumBars - 2 + b]); };
+  auto bar_drain = [&](int b) { return smem_u32(&bars[kNumBars - 4 + b]); };
 
   if (tid == 0) {
     for (int s = 0; s < kXStagesMax; ++s) { mbar_init(bar_xfull(s), 1); mbar_init(bar_xconv(s), 4); mbar_init(bar_xempty(s), 1); }
     for (int s = 0; s < kWStagesMax; ++s) mbar_init(bar_wfull(s), 1);
     for (int s = 0; s < kAStages; ++s) mbar_init(bar_afull(s), 1);
     for (int c = 0; c < kGroups; ++c) mbar_init(bar_gdone(c), 1);
-    for (int b = 0; b < 2; ++b) mbar_init(bar_pempty(b), 8);
-    *abort_flag = 0;
+    for (int b = 0; b < 2; ++b) { mbar_init(bar_pempty(b), 8); mbar_init(bar_drain(b), 1); }
+    abort_flag[0] = 0;
+    abort_flag[1] = (int)(p.spin_limit ? p.spin_limit : kSpinLimit);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // the whole tensor memory of the SM: this kernel runs one CTA per SM
@@ -282,7 +297,7 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
     // ---- activation loads: one patch (tile + halo) per 32-channel chunk ----
     if (lane == 0) {
       const uint32_t box_bytes = (uint32_t)p.box_rows * 128u;
-      int s = 0;
+      int s = 0, loads = 0;
       uint32_t phase = 1;  // (a fresh barrier lets the first lap through)
       bool ok = true;
       for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
@@ -291,6 +306,10 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
         decode(it.tile, w0, h0, n0, oc0);
         for (int chunk = it.chunk0; chunk < it.chunk0 + it.chunks; ++chunk) {
           if (!(ok = TIMED(0, mbar_wait(bar_xempty(s), phase, abort_flag)))) break;
+          if (loads++ == 0 && p.withhold_first_load) {  // (test: this patch never arrives, its readers give up)
+            if (++s == p.n_x) { s = 0; phase ^= 1u; }
+            continue;
+          }
           mbar_expect_tx(bar_xfull(s), box_bytes);
           if (p.linear)
             tma_load_4d(smem_u32(xbase + (size_t)s * p.x_stage_bytes), &map_x, bar_xfull(s), chunk * KC, (w0 / kTW) * BM, 0, 0);
@@ -301,6 +320,10 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
             tma_load_4d(smem_u32(xbase + (size_t)s * p.x_stage_bytes), &map_x, bar_xfull(s), chunk * KC, w0 - p.P, h0 - p.P, n0);
           if (++s == p.n_x) { s = 0; phase ^= 1u; }
         }
+      }
+      if (!ok || *abort_flag) {  // the loads of the last lap may still be in flight
+        for (int v = max(loads - p.n_x, p.withhold_first_load ? 1 : 0); v < loads; ++v)
+          mbar_drain(bar_xfull(v % p.n_x), (uint32_t)(v / p.n_x) & 1u);
       }
       PROF_OUT(0);
     }
@@ -323,6 +346,9 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
           mbar_expect_tx(bar_wfull(s), bytes);
           bulk_load(smem_u32(wbase + (size_t)s * U * kWBytes), item + (size_t)(U * j) * (BN * 64), bytes, bar_wfull(s));
         }
+      }
+      if (!ok || *abort_flag) {  // the copies of the last lap may still be in flight
+        for (int v = max(G - p.n_w, 0); v < G; ++v) mbar_drain(bar_wfull(v % p.n_w), (uint32_t)(v / p.n_w) & 1u);
       }
       PROF_OUT(1);
     }
@@ -398,6 +424,11 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
         __syncwarp();
       }
     }
+    if (!ok || *abort_flag) {  // the copies issued so far may still be running
+      if (elect_one()) umma_commit(bar_drain(0));
+      __syncwarp();
+      mbar_drain(bar_drain(0), 0);
+    }
     PROF_OUT(2);
   } else if (warp == 1) {
     // ---- MMA issue (converged warp, one elected lane): six tcgen05.mma per K step, one wait and
@@ -450,6 +481,11 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
         }
         __syncwarp();
       }
+    }
+    if (!ok || *abort_flag) {  // the MMAs issued so far may still be running
+      if (elect_one()) umma_commit(bar_drain(1));
+      __syncwarp();
+      mbar_drain(bar_drain(1), 0);
     }
     PROF_OUT(3);
   } else if (warp >= 4 && warp < 8) {
@@ -997,6 +1033,7 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
     bn = t->bn;
   }
   p.out = out;
+  p.withhold_first_load = test_injection(&p.spin_limit);
 #ifdef TETRIS_TC16_PROF
   static long long *d_prof = nullptr;
   const bool prof = getenv("TETRIS_TC16_PROF") != nullptr;
@@ -1052,7 +1089,12 @@ int conv_tc16_check_error(const tetris_filter *f) {
   if (!t) return 0;
   int flag = 0;
   if (cudaMemcpy(&flag, t->d_error, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return 1;
-  if (flag) cudaMemset(t->d_error, 0, sizeof(int));
+  if (flag) {
+    // (a launch that gave up may have left the guard's words and the last-wave counters half way)
+    cudaMemset(t->d_error, 0, sizeof(int));
+    cudaMemset(t->d_gate, 0, 2 * sizeof(unsigned));
+    cudaMemset(t->d_tail_count, 0, (size_t)t->sms * sizeof(int));
+  }
   return flag;
 }
 

@@ -84,6 +84,9 @@ void tiled_plans_export(const tetris_filter *f, std::vector<int32_t> *out);
 void tiled_plans_import(const tetris_filter *f, const int32_t *plans, int n);
 // conv kernel launches issued through the library by this process (all devices, all threads)
 void count_launch();
+// tetris_test_inject (failure-detection tests): 1 while the tensor-core kernels are asked to leave
+// out every CTA's first activation load, with the poll limit their barrier waits then use.
+int test_injection(unsigned *spin_limit);
 void tiled_plan_cache_delete(void *cache);
 int conv_tc_prepare(tetris_filter *f, const float *d_dense);
 void conv_tc_state_delete(void *state);
