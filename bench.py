@@ -32,8 +32,8 @@ from __graft_entry__ import load_package  # noqa: E402
 # of a launch over the algorithmic bytes of the captured layer); the bench scales it to its own
 # mean launch.  The captures are summarised under profiles/.
 NCU_TRAFFIC = {
-    "tensor16_3x3_s1": {"dram_over_algorithmic": 65.0 / 107.5,
-                        "note": "captured on VGG-19 conv3_3 batch 16: 65.0 MB per launch against 107.5 MB "
+    "tensor16_3x3_s1": {"dram_over_algorithmic": 67.9 / 107.5,
+                        "note": "captured on VGG-19 conv3_3 batch 16: 67.9 MB per launch against 107.5 MB "
                                 "algorithmic (outputs still in L2 at kernel end); scaled by algorithmic bytes"},
     "tensor_3x3_s1": {"dram_over_algorithmic": 65.7 / 107.5,
                       "note": "captured on VGG-19 conv3_3 batch 16: 65.7 MB per launch against 107.5 MB "
