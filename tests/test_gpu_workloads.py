@@ -4,7 +4,8 @@ Two sweeps:
 
 * `test_layer_batch1_and_batch2`: each layer of `single`, `vgg19`, `resnet50`, `mobilenet` and
   `yolov3` at batch 1 and batch 2 (odd and even image pairing, images packed into one tile on
-  the small late layers) through the automatic choice *after* tuning -- the configuration the
+  the small late layers; plus `vgg19_s99`, VGG-19 pruned to 99 %, where the tuner picks the list
+  kernel on several layers) through the automatic choice *after* tuning -- the configuration the
   benchmark times -- and through the forced tensor-core and list kernels where they cover the
   shape.  The whole output is compared with the oracle (HostConv2d, Tetris/tensor_utils.cc:136-170;
   per-plane for the depthwise layers).
@@ -35,7 +36,7 @@ def _catalogue():
 
 
 _WL = _catalogue()
-SWEEP = [(w, i) for w in ("single", "vgg19", "resnet50", "mobilenet", "yolov3")
+SWEEP = [(w, i) for w in ("single", "vgg19", "resnet50", "mobilenet", "yolov3", "vgg19_s99")
          for i in range(len(_WL.WORKLOADS[w]()))]
 FULL = [(w, i) for w in ("vgg19", "yolov3") for i in range(len(_WL.WORKLOADS[w]()))]
 

@@ -40,6 +40,15 @@ def vgg19():
     return layers
 
 
+def vgg19_s99():
+    """VGG-19's shapes pruned to 99 % (first layer 50 %): not one of the five benchmark workloads.
+    It shows where the per-layer choice crosses over: the list kernel's time falls with the
+    nonzeros until staging the input tiles is all that is left, and at 99 % it meets the dense
+    tensor-core kernels (whose time does not depend on the mask) on the 224x224 and 56x56 layers,
+    where the tuner then picks it."""
+    return [l._replace(sparsity=0.50 if i == 0 else 0.99) for i, l in enumerate(vgg19())]
+
+
 def resnet50():
     layers = [Layer("stem", 224, 224, 3, 64, 7, 3, 2, 1, 0.50)]
     size, ic = 56, 64  # after the stem (112) and the 3x3/2 max-pool
@@ -152,6 +161,7 @@ WORKLOADS = {
     "mobilenet": mobilenet_v1,
     "yolov3": yolov3,
     "real": real_layers,
+    "vgg19_s99": vgg19_s99,
 }
 
 
