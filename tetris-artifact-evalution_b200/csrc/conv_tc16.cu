@@ -665,13 +665,16 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
       row_ok = row_ok && !*abort_flag;
       const int ocb = oc0 + half * NC;
       float *o = p.out + pix * p.OC + ocb;
+      const bool coalesced = vec && ocb + NC <= p.OC && small_out;
+      if (!coalesced) {  // (the coalesced path scales after the rows are turned: two loads per thread instead of NC)
 #pragma unroll
-      for (int j = 0; j < NC; ++j) acc[j] *= (ocb + j < p.OC) ? __ldg(p.out_scale + ocb + j) : 0.f;
-      if (p.relu) {
+        for (int j = 0; j < NC; ++j) acc[j] *= (ocb + j < p.OC) ? __ldg(p.out_scale + ocb + j) : 0.f;
+        if (p.relu) {
 #pragma unroll
-        for (int j = 0; j < NC; ++j) acc[j] = fmaxf(acc[j], 0.f);
+          for (int j = 0; j < NC; ++j) acc[j] = fmaxf(acc[j], 0.f);
+        }
       }
-      if (vec && ocb + NC <= p.OC && small_out) {
+      if (coalesced) {
         // Coalesced path: a thread holds 32..64 channels of ONE pixel; through a 4 KiB staging
         // block per warp the rows are turned so that eight lanes write one pixel's 128
         // contiguous bytes (4 passes through the memory pipe per store instead of 32).
@@ -686,10 +689,14 @@ conv_tc16_kernel(const __grid_constant__ CUtensorMap map_x, const Tc16Params p) 
           __syncwarp();
           float4 v[8];
           const int qq = lane & 7;
+          // this lane's four channels of every row: the per-channel scale (a power of two, exact)
+          const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.out_scale + ocb + h * 32 + 4 * qq));
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int r = 4 * i + (lane >> 3);
             v[i] = stage[r * 8 + (qq ^ (r & 7))];
+            v[i].x *= sc.x; v[i].y *= sc.y; v[i].z *= sc.z; v[i].w *= sc.w;
+            if (p.relu) { v[i].x = fmaxf(v[i].x, 0.f); v[i].y = fmaxf(v[i].y, 0.f); v[i].z = fmaxf(v[i].z, 0.f); v[i].w = fmaxf(v[i].w, 0.f); }
           }
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -1003,8 +1010,10 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
       if (best_d == 1 && tiles > sms && sms <= t->sms) {
         const int full = (int)(tiles / sms) * sms, rest = (int)tiles - full;
         int d = 0;
+        // (writing the slices out and adding them up costs a tile about as much as 30 K steps:
+        // the split has to save more than that)
         for (int c = 2; c <= 8 && c <= q.n_chunks; ++c)
-          if (q.n_chunks % c == 0 && rest * c <= sms) d = c;
+          if (q.n_chunks % c == 0 && rest * c <= sms && iters * (c - 1) >= 32.0 * c) d = c;
         if (rest > 0 && d >= 2) { q.tail_tile0 = full; q.tail_start = full; q.tail_d = d; }
       }
       // shared memory: activation ring, weight ring, store staging, barriers
@@ -1019,7 +1028,7 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
       }
       if (q.n_x < 2) { set_error("split-FP16 variant: the activation patches of this layer do not fit shared memory"); return TETRIS_ERR_UNSUPPORTED; }
       if (KS > 1) q.n_x = std::min(q.n_x, 3);          // a patch feeds KS*KS steps: three stages are ample
-      q.n_x = std::max(2, std::min(q.n_x, std::max(2, chunks_per_item)));
+      q.n_x = std::max(2, std::min(q.n_x, std::max(3, 2 * chunks_per_item)));  // (patches are fetched across work items)
       su->smem = fixed + (size_t)q.n_x * q.x_stage_bytes + (size_t)q.n_w * wbytes;
       su->grid = dim3((unsigned)std::min<long long>(q.tail_start + (tiles - q.tail_tile0) * q.tail_d, sms));  // persistent: one CTA per SM
       su->in = in;
