@@ -421,7 +421,7 @@ def test_tensor16_value_ranges(tb, torch_cuda, oracle):
     bad, max_rel, _ = oracle.compare(got, oracle.host_conv2d(x, filt, 1, 1))
     assert bad == 0, "plain launch after an out-of-range one: %d elements off (max rel %.3g)" % (bad, max_rel)
     # output channels whose weights differ by seven orders of magnitude share one filter-wide
-    # scale; each channel is judged by the bar of the path with the floor scaled like its weights
+    # scale; each channel is held to the bar of the path with the floor scaled like its weights
     # (against a floor of 1e-5 the CPU path's own FP32 rounding would show on the large channels)
     chan = np.exp(rng.uniform(np.log(2e-5), np.log(600.0), (oc, 1, 1, 1))).astype(np.float32)
     wide = filt * chan

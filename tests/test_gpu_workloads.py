@@ -53,7 +53,7 @@ def _report(record):
             fh.write(json.dumps(record) + "\n")
 
 
-def _judge(oracle, got, want, what):
+def _assess(oracle, got, want, what):
     assert not np.isnan(got).any(), "%s: output elements were left unwritten" % what
     bad, max_rel, n_floor = oracle.compare(got, want)
     assert bad == 0, "%s: %d of %d elements outside 1e-4*|y| + 1e-5 (max rel %.3g)" % (
@@ -99,7 +99,7 @@ def test_layer_batch1_and_batch2(tb, torch_cuda, oracle, case):
             torch.cuda.synchronize()
             f.check()
             got = out.cpu().numpy().transpose(0, 3, 1, 2)
-            rec = _judge(oracle, got, want[lo:hi], "%s %s batch %d %s" % (workload, L.name, n, label))
+            rec = _assess(oracle, got, want[lo:hi], "%s %s batch %d %s" % (workload, L.name, n, label))
             rec.update(workload=workload, layer=L.name, batch=n, variant=label)
             if tuned:
                 rec["kernel"] = tb.auto_choice(f, n, L.H, L.W, L.stride, L.pad)
@@ -134,7 +134,7 @@ def test_full_size_batch16_slice(tb, torch_cuda, oracle, case):
     xs = x[imgs].permute(0, 3, 1, 2).contiguous().cpu().numpy()
     want = oracle.host_conv2d(xs, filt[oc0:oc1], L.stride, L.pad, threads=True, skip_zero=True)
     got = out[imgs][..., oc0:oc1].permute(0, 3, 1, 2).contiguous().cpu().numpy()
-    rec = _judge(oracle, got, want, "%s %s batch 16 channels %d..%d" % (workload, L.name, oc0, oc1))
+    rec = _assess(oracle, got, want, "%s %s batch 16 channels %d..%d" % (workload, L.name, oc0, oc1))
     rec.update(workload=workload, layer=L.name, batch=n, variant="auto_tuned",
                kernel=tb.auto_choice(f, n, L.H, L.W, L.stride, L.pad), oc_slice=[oc0, oc1])
     _report(rec)
