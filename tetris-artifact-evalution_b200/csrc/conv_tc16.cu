@@ -808,7 +808,7 @@ struct Tc16State {
   unsigned *d_gate = nullptr;
   int n_chunks = 0, bn = 128;
   float *d_out_scale = nullptr;  // per output channel
-  float *d_scratch = nullptr;    // tail split: one 128 x BN block of partial sums per CTA
+  float *d_scratch = nullptr;    // tail split: one 128 x BN block of partial sums per CTA (allocated when a shape first needs it)
   int *d_tail_count = nullptr;   // tail split: finished slices per last-wave tile (all zero between launches)
   int sms = 0;
   struct Setup {
@@ -854,7 +854,6 @@ int conv_tc16_prepare(tetris_filter *f, const float *d_dense) {
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&s->sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) s->sms = 0;
   if (s->sms < 1 || cudaMalloc(&s->d_tiles, elems * sizeof(__half)) != cudaSuccess || cudaMalloc(&s->d_error, sizeof(int)) != cudaSuccess ||
       cudaMalloc(&s->d_gate, 2 * sizeof(unsigned)) != cudaSuccess ||
-      cudaMalloc(&s->d_scratch, (size_t)s->sms * BM * s->bn * sizeof(float)) != cudaSuccess ||
       cudaMalloc(&s->d_tail_count, (size_t)s->sms * sizeof(int)) != cudaSuccess) {
     cudaGetLastError();
     conv_tc16_state_delete(s);
@@ -1014,7 +1013,13 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
         // the split has to save more than that)
         for (int c = 2; c <= 8 && c <= q.n_chunks; ++c)
           if (q.n_chunks % c == 0 && rest * c <= sms && iters * (c - 1) >= 32.0 * c) d = c;
-        if (rest > 0 && d >= 2) { q.tail_tile0 = full; q.tail_start = full; q.tail_d = d; }
+        if (rest > 0 && d >= 2 && !t->d_scratch &&  // (10 MB per filter: only for filters that have such a shape)
+            cudaMalloc(&t->d_scratch, (size_t)t->sms * BM * t->bn * sizeof(float)) != cudaSuccess) {
+          cudaGetLastError();
+          t->d_scratch = nullptr;
+          d = 0;
+        }
+        if (rest > 0 && d >= 2) { q.tail_tile0 = full; q.tail_start = full; q.tail_d = d; q.scratch = t->d_scratch; }
       }
       // shared memory: activation ring, weight ring, store staging, barriers
       const size_t wbytes = (size_t)t->bn * 128 * group_steps(t->bn, KS);  // a weight stage holds a group of K steps
