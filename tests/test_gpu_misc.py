@@ -5,15 +5,25 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("n,c,h,w,stride", [(2, 32, 20, 20, 1), (1, 64, 15, 17, 2), (3, 7, 5, 4, 1)])
-def test_depthwise_against_oracle(tb, torch_cuda, oracle, n, c, h, w, stride):
-    rng = np.random.default_rng(c)
+# (n, c, h, w, stride, pad): channel counts that are multiples of 32 take the pipelined kernel
+# (16-wide tiles, 8-wide tiles for images up to 8 wide, stride 2), the others the plain kernels
+@pytest.mark.parametrize("n,c,h,w,stride,pad", [
+    (2, 32, 20, 20, 1, 1), (1, 64, 15, 17, 2, 1), (3, 7, 5, 4, 1, 1),
+    (2, 96, 7, 7, 1, 1), (1, 32, 8, 30, 1, 1), (2, 64, 33, 47, 1, 0), (3, 32, 9, 9, 2, 0),
+    (16, 128, 56, 56, 1, 1),   # more tiles than CTAs: the ring of stages turns several times
+    (16, 64, 57, 55, 2, 1), (2, 24, 19, 21, 2, 1), (1, 36, 6, 40, 1, 1), (1, 32, 1, 1, 1, 1)])
+def test_depthwise_against_oracle(tb, torch_cuda, oracle, n, c, h, w, stride, pad):
+    rng = np.random.default_rng(c * 100 + h)
     filt = rng.normal(0, 0.05, (c, 1, 3, 3)).astype(np.float32)
-    x = rng.random((n, c, h, w), dtype=np.float32)
+    x = (rng.random((n, c, h, w), dtype=np.float32) - 0.25).astype(np.float32)
     f = tb.SparseFilter(filt, c, c, 3, groups=c)
-    got = tb.cuda_sparse_conv2d(x, f, n, h, w, stride, 1)
-    bad, max_rel, _ = oracle.compare(got, oracle.host_depthwise_conv2d(x, filt, stride, 1))
-    assert bad == 0, max_rel
+    want = oracle.host_depthwise_conv2d(x, filt, stride, pad)
+    for _ in range(2):   # (the second call finds its tensor map in the cache)
+        got = tb.cuda_sparse_conv2d(x, f, n, h, w, stride, pad)
+        f.check()
+        bad, max_rel, _ = oracle.compare(got, want)
+        assert bad == 0, max_rel
+    f.close()
 
 
 @pytest.mark.parametrize("shape", [(2, 5, 4, 3), (1, 64, 33, 31), (3, 3, 70, 9), (2, 130, 1, 1)])

@@ -386,6 +386,10 @@ int tetris_filter_check(const tetris_filter_t *f) {
     set_error("device error: %s", cudaGetErrorString(cudaGetLastError()));
     return TETRIS_ERR_CUDA;
   }
+  if (f->groups != 1 && depthwise_check_error()) {
+    set_error("a depthwise launch gave up on a bounded barrier wait; its output is invalid");
+    return TETRIS_ERR_CUDA;
+  }
   if (conv_tc_check_error(f) | conv_tc16_check_error(f)) {
     set_error("a tensor-core launch of this filter gave up on a bounded barrier wait; its output is invalid");
     return TETRIS_ERR_CUDA;

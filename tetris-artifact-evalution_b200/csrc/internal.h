@@ -103,6 +103,7 @@ int launch_conv_tc16(const tetris_filter *f, const float *in, float *out, const 
 int conv_tc16_check_error(const tetris_filter *f);
 int launch_depthwise(const tetris_filter *f, const float *in, float *out, const ConvShape &s,
                      cudaStream_t st);
+int depthwise_check_error();
 // chain.cu / api.cu: y = max(y, 0) in place; an automatic launch of one conv (with its fused
 // options in s); whether the launch at hand rectified at its own store
 int launch_relu_inplace(float *y, size_t n, cudaStream_t st);
