@@ -66,6 +66,8 @@
 // IC % 4 == 0.
 #include <cuda.h>
 
+#include <cstring>
+
 #include <algorithm>
 #include <cstdlib>
 #include <mutex>
@@ -116,6 +118,7 @@ struct TcParams {
   int relu;                    // max(y, 0) at the store (never together with a split K range)
   int *error_flag;
   const float *w_tiles;        // weight tile images, see tc_weight_tiles_kernel
+  int tma_store;               // the summing warps hand their staged blocks to TMA stores (see the epilogue)
   unsigned spin_limit;         // polls after which a barrier wait gives up (0: kSpinLimit)
   int withhold_first_load;     // failure-detection test only: every CTA leaves out its first activation load
   unsigned *gate;              // when set: the launch runs only if the magnitude in gate[0] asks for it (see launch_conv_tc_gated)
@@ -218,7 +221,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_out, const TcParams p) {
   extern __shared__ unsigned char smem_raw[];
   // A gated launch stands behind the split-FP16 variant, which left the largest |activation| it
   // saw (FP32 bits) in gate[0].  Recompute the layer when that does not fit FP16's window
@@ -645,6 +648,35 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
       const bool row_ok = pn < p.NB && ow < p.OW && oh < p.OH && n < p.N && !*abort_flag;
       const int ocb = oc0 + half * NC;
       float *o = p.out + (((size_t)n * p.OH + oh) * p.OW + ow) * p.OC + ocb;
+      if (p.tma_store) {
+        // Short K ranges, tiles of one image with 32 % TW == 0 that are 128 pixels large or span
+        // the image's height: the 32 rows of a warp are 32 / TW whole tile rows, so the warp's 4 KiB
+        // staging block -- 32 rows of 32 channels in the 128-byte swizzle -- is exactly a box
+        // {32 channels, TW, 32 / TW, 1} of the NHWC output.  One lane hands it to a TMA store
+        // and the warp carries on: the store's shared-memory reads and global writes run
+        // behind the next tile's sums (loading the rows back and storing them with the LSU took
+        // the warps ~3000 clocks per tile, more than the MMAs of a two-step K range).  Rows and
+        // channels outside the tensor are dropped by the store.
+        float4 *stage = reinterpret_cast<float4 *>(store_base + (warp - 12) * 4096);
+#pragma unroll
+        for (int h = 0; h < NC / 32; ++h) {
+          if (ocb + h * 32 >= p.OC) break;
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the block's last store has read it
+          __syncwarp();
+#pragma unroll
+          for (int qq = 0; qq < 8; ++qq)
+            stage[lane * 8 + (qq ^ (lane & 7))] = make_float4(acc[h * 32 + 4 * qq], acc[h * 32 + 4 * qq + 1],
+                                                               acc[h * 32 + 4 * qq + 2], acc[h * 32 + 4 * qq + 3]);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0 && !*abort_flag) {
+            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                         ::"l"(&map_out), "r"(smem_u32(stage)), "r"(ocb + h * 32), "r"(w0), "r"(h0 + quarter * (32 / p.TW)), "r"(n0) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+        continue;
+      }
       if (vec && ocb + NC <= p.OC && small_out && p.w_stages == 4) {
         // Coalesced path.  A thread holds 32..64 channels of ONE pixel, so stored directly the
         // 32 lanes of an instruction hit 32 different lines (32 passes through the memory pipe
@@ -714,6 +746,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcParams p) {
           if (ocb + j < p.OC) o[j] = acc[j];
       }
     }
+    if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // this warp's stores are complete
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -790,8 +823,9 @@ struct TcState {
     bool valid = false;
     bool gated = false;          // set-ups of gated launches never split the K range
     const float *in = nullptr;
+    const float *out = nullptr;  // (the output's tensor map belongs to the set-up too)
     ConvShape shape{};
-    CUtensorMap map_x;
+    CUtensorMap map_x, map_out;
     TcParams params{};
     dim3 grid;
   };
@@ -872,7 +906,7 @@ int launch_conv_tc_impl(const tetris_filter *f, const float *in, float *out, con
     set_error("tensor-core variant covers strides up to 8, in_channel <= 4 or a multiple of 4, 16-byte aligned inputs");
     return TETRIS_ERR_UNSUPPORTED;
   }
-  CUtensorMap map_x;
+  CUtensorMap map_x, map_out;
   TcParams p;
   dim3 grid;
   int bn = 128;
@@ -881,7 +915,7 @@ int launch_conv_tc_impl(const tetris_filter *f, const float *in, float *out, con
     TcState::Setup *su = nullptr;
     for (TcState::Setup &c : t->setups) {
       const ConvShape &l = c.shape;
-      if (c.valid && c.in == in && c.gated == (gate != nullptr) && l.relu == s.relu && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S) { su = &c; break; }
+      if (c.valid && c.in == in && c.out == out && c.gated == (gate != nullptr) && l.relu == s.relu && l.N == s.N && l.H == s.H && l.W == s.W && l.P == s.P && l.S == s.S) { su = &c; break; }
     }
     if (!su) {
       su = &t->setups[t->next_setup];
@@ -894,6 +928,7 @@ int launch_conv_tc_impl(const tetris_filter *f, const float *in, float *out, con
       const int halo = per_tap ? 0 : s.KS - 1;
       int best_tw = 0, best_th = 1, best_nb = 1;
       double best = -1.0;
+      bool best_boxy = false;
       for (int TW = 1; TW <= std::min(s.OW, 128); ++TW) {
         int TH = std::min(s.OH, 128 / TW);
         while (TH > 1 && (TW + halo) * (TH + halo) > kPatchRows) --TH;
@@ -902,7 +937,11 @@ int launch_conv_tc_impl(const tetris_filter *f, const float *in, float *out, con
         while (NB > 1 && (TW + halo) * (TH + halo) * NB > kPatchRows) --NB;
         const double tiles = (double)((s.OW + TW - 1) / TW) * ((s.OH + TH - 1) / TH) * ((s.N + NB - 1) / NB);
         const double eff = (double)s.N * s.OH * s.OW / (tiles * 128.0);
-        if (eff > best) { best = eff; best_tw = TW; best_th = TH; best_nb = NB; }
+        // (among equally full tiles, one whose rows fill a warp's 32 lanes: see tma_store below)
+        // (a tile shorter than 128 rows qualifies when it spans the image's height: the rows past
+        // its end then lie below the image and the store drops them)
+        const bool boxy = NB == 1 && 32 % TW == 0 && (TW * TH == 128 || TH == s.OH);
+        if (eff > best + 1e-9 || (eff > best - 1e-9 && boxy && !best_boxy)) { best = eff; best_tw = TW; best_th = TH; best_nb = NB; best_boxy = boxy; }
       }
       if (best_tw == 0) {
         set_error("tensor-core variant: no tile of this layer fits an activation stage");
@@ -953,14 +992,28 @@ int launch_conv_tc_impl(const tetris_filter *f, const float *in, float *out, con
       // Few K steps per work item: the epilogue weighs more than a deep weight ring (measured:
       // 18-step tiles 8 % faster with the staged stores, 144-step tiles 13 % slower on 4 stages).
       q.w_stages = iters / best_d <= 40.0 ? 4 : 5;
+      // TMA stores from the staging blocks (see the kernel's epilogue): short K ranges on large
+      // images, whole tiles of one image whose rows fill a warp's 32 lanes
+      q.tma_store = 0;
+      std::memset(&su->map_out, 0, sizeof(su->map_out));
+      if (q.w_stages == 4 && best_d == 1 && best_nb == 1 && 32 % best_tw == 0 && (best_tw * best_th == 128 || best_th == s.OH) &&
+          (s.OC & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        const cuuint64_t odims[4] = {(cuuint64_t)s.OC, (cuuint64_t)s.OW, (cuuint64_t)s.OH, (cuuint64_t)s.N};
+        const cuuint64_t ostrides[3] = {(cuuint64_t)s.OC * 4, (cuuint64_t)s.OC * 4 * s.OW, (cuuint64_t)s.OC * 4 * s.OW * s.OH};
+        const cuuint32_t obox[4] = {32, (cuuint32_t)best_tw, (cuuint32_t)(32 / best_tw), 1};
+        const cuuint32_t oestr[4] = {1, 1, 1, 1};
+        if (encode_map(&su->map_out, out, 4, odims, ostrides, obox, oestr) == TETRIS_OK) q.tma_store = 1;
+      }
       const long long total = tiles * best_d;
       su->grid = dim3((unsigned)std::min<long long>(total, sms));  // persistent: one CTA per SM
       su->in = in;
+      su->out = out;
       su->gated = gate != nullptr;
       su->shape = s;
       su->valid = true;
     }
     map_x = su->map_x;
+    map_out = su->map_out;
     p = su->params;
     grid = su->grid;
     bn = t->bn;
@@ -981,9 +1034,9 @@ int launch_conv_tc_impl(const tetris_filter *f, const float *in, float *out, con
   if (p.ksplit > 1)  // the work items add into the output
     TETRIS_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)s.N * s.OH * s.OW * s.OC * sizeof(float), st));
   if (bn == 64)
-    conv_tc_kernel<64><<<grid, kThreads, smem, st>>>(map_x, p);
+    conv_tc_kernel<64><<<grid, kThreads, smem, st>>>(map_x, map_out, p);
   else
-    conv_tc_kernel<128><<<grid, kThreads, smem, st>>>(map_x, p);
+    conv_tc_kernel<128><<<grid, kThreads, smem, st>>>(map_x, map_out, p);
   TETRIS_CUDA_TRY(cudaGetLastError());
   if (!gate) count_launch();
   if (p.relu) note_relu_fused();
