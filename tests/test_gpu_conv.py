@@ -551,3 +551,39 @@ def test_bounded_wait_gives_up_and_the_next_launch_passes(tb, torch_cuda, oracle
     bad, max_rel, _ = oracle.compare(got, want)
     assert bad == 0, "%d elements differ after the recovery (max rel %.3g)" % (bad, max_rel)
     f.close()
+
+
+@pytest.mark.parametrize("case", [
+    # (n, ic, h, w, oc, ks, pad): 1x1 and short-K layers on images whose tiles take the TMA-store epilogue of the
+    # split-TF32 kernel: 128-pixel tiles, tiles that span the image's height, channel counts that end inside a
+    # 32-channel box, images that end inside a tile
+    (3, 64, 32, 32, 36, 1, 0), (2, 32, 32, 32, 96, 1, 0), (2, 64, 40, 24, 100, 1, 0), (1, 128, 12, 40, 64, 1, 0),
+    (2, 16, 50, 44, 256, 1, 0), (16, 64, 56, 56, 256, 1, 0), (2, 8, 30, 64, 32, 3, 1), (1, 96, 7, 32, 160, 1, 0)])
+@pytest.mark.parametrize("relu", [False, True])
+def test_tensor_variant_short_k_store_path(tb, torch_cuda, oracle, case, relu):
+    torch = torch_cuda
+    n, ic, h, w, oc, ks, pad = case
+    rng = np.random.default_rng(n * 1000 + oc)
+    filt = (rng.standard_normal((oc, ic, ks, ks)) * 0.1 * (rng.random((oc, ic, ks, ks)) >= 0.7)).astype(np.float32)
+    x = (rng.random((n, ic, h, w), dtype=np.float32) - 0.3).astype(np.float32)
+    imgs = [0, n - 1] if n > 2 else list(range(n))
+    want = oracle.host_conv2d(x[imgs], filt, 1, pad, threads=True, skip_zero=True)
+    if relu:
+        want = np.maximum(want, 0)
+    f = tb.SparseFilter(filt, ic, oc, ks)
+    xin = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).cuda()
+    oh, ow = want.shape[2], want.shape[3]
+    out = torch.full((n, oh, ow, oc), float("nan"), device="cuda")
+    for _ in range(2):
+        out.fill_(float("nan"))
+        if relu:
+            tb.sparse_conv2d_fused(f, xin, out, n, h, w, 1, pad, variant=VARIANTS["tensor"], relu=True)
+        else:
+            tb.sparse_conv2d(f, xin, out, n, h, w, 1, pad, variant=VARIANTS["tensor"])
+        torch.cuda.synchronize()
+        f.check()
+        got = out[imgs].cpu().numpy().transpose(0, 3, 1, 2)
+        assert not np.isnan(out.cpu().numpy()).any(), "output elements were left unwritten"
+        bad, max_rel, _ = oracle.compare(got, want)
+        assert bad == 0, "%d elements differ (max rel %.3g)" % (bad, max_rel)
+    f.close()
